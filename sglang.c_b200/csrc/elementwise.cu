@@ -99,10 +99,13 @@ SGLC_API int sglc_xielu(const void* src, long long src_stride, int src_dtype, vo
 //   dst[r][j] = silu(src[r][j]) * src[r][F + j] * (w ? w[r][j / per] : 1),   j < F
 // src holds the F gate columns, then the F up columns.  With `w` (float [rows][F / per]) a block of
 // `per` columns is one expert of a mixture and takes the token's weight for it (zero: not chosen).
+// `act` chooses the gate's function (silu, or the tanh form of GELU); `mult` is one more factor of
+// every result (a layer's residual multiplier, taken in 32-bit ahead of the rounding).
+enum { GA_SILU = 0, GA_GELU_TANH = 1 };
 template <typename TI, typename TO>
 __global__ void gated_act_kernel(const TI* __restrict__ src, long long src_stride, TO* __restrict__ dst,
                                  long long dst_stride, int rows, int F, const float* __restrict__ w,
-                                 long long w_stride, int per) {
+                                 long long w_stride, int per, int act, float mult) {
   pdl_launch_dependents();
   pdl_wait();
   const long long total = (long long)rows * F;
@@ -114,7 +117,7 @@ __global__ void gated_act_kernel(const TI* __restrict__ src, long long src_strid
     float out = 0.0f;
     if (wt != 0.0f) {
       const float g = to_f32(src[r * src_stride + c]), u = to_f32(src[r * src_stride + F + c]);
-      out = g / (1.0f + expf(-g)) * u * wt;
+      out = (act == GA_GELU_TANH ? gelu_tanh_f32(g) : g / (1.0f + expf(-g))) * u * (wt * mult);
     }
     dst[r * dst_stride + c] = from_f32<TO>(out);
   }
@@ -124,7 +127,7 @@ __global__ void gated_act_kernel(const TI* __restrict__ src, long long src_strid
 // multiples of 8, rows 16-byte aligned
 __global__ void gated_act_vec8_kernel(const __nv_bfloat16* __restrict__ src, long long src_stride,
                                       __nv_bfloat16* __restrict__ dst, long long dst_stride, int rows, int F,
-                                      const float* __restrict__ w, long long w_stride, int per) {
+                                      const float* __restrict__ w, long long w_stride, int per, int act, float mult) {
   pdl_launch_dependents();
   pdl_wait();
   const int F8 = F / 8;
@@ -133,7 +136,7 @@ __global__ void gated_act_vec8_kernel(const __nv_bfloat16* __restrict__ src, lon
        i += (long long)gridDim.x * blockDim.x) {
     const long long r = i / F8;
     const int c = (int)(i % F8) * 8;
-    const float wt = w ? w[r * w_stride + c / per] : 1.0f;
+    const float wt = (w ? w[r * w_stride + c / per] : 1.0f) * mult;
     uint4 o = make_uint4(0u, 0u, 0u, 0u);
     if (wt != 0.0f) {
       const uint4 g4 = *reinterpret_cast<const uint4*>(src + r * src_stride + c);
@@ -144,17 +147,21 @@ __global__ void gated_act_vec8_kernel(const __nv_bfloat16* __restrict__ src, lon
 #pragma unroll
       for (int k = 0; k < 4; k++) {
         const float2 g = __bfloat1622float2(gp[k]), u = __bfloat1622float2(up[k]);
-        op[k] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x * wt, g.y / (1.0f + expf(-g.y)) * u.y * wt);
+        if (act == GA_GELU_TANH)
+          op[k] = __floats2bfloat162_rn(gelu_tanh_f32(g.x) * u.x * wt, gelu_tanh_f32(g.y) * u.y * wt);
+        else
+          op[k] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x * wt, g.y / (1.0f + expf(-g.y)) * u.y * wt);
       }
     }
     *reinterpret_cast<uint4*>(dst + r * dst_stride + c) = o;
   }
 }
 
-SGLC_API int sglc_gated_act(const void* src, long long src_stride, int src_dtype, void* dst, long long dst_stride,
-                            int dst_dtype, int rows, int F, const float* w, long long w_stride, int per,
-                            cudaStream_t stream) {
+SGLC_API int sglc_gated_act_ext(const void* src, long long src_stride, int src_dtype, void* dst, long long dst_stride,
+                                int dst_dtype, int rows, int F, const float* w, long long w_stride, int per,
+                                int act, float mult, cudaStream_t stream) {
   if (rows <= 0 || F <= 0) return SGLC_OK;
+  if (act != GA_SILU && act != GA_GELU_TANH) return SGLC_ERR_ARGUMENT;
   if (w && (per <= 0 || F % per != 0)) return SGLC_ERR_ARGUMENT;
   const long long total = (long long)rows * F;
   int blocks = (int)((total + 255) / 256);
@@ -164,14 +171,51 @@ SGLC_API int sglc_gated_act(const void* src, long long src_stride, int src_dtype
     int b8 = (int)((total / 8 + 255) / 256);
     if (b8 > 148 * 16) b8 = 148 * 16;
     return sglc_launch(gated_act_vec8_kernel, dim3(b8), dim3(256), 0, stream, 1, true, (const __nv_bfloat16*)src,
-                       src_stride, (__nv_bfloat16*)dst, dst_stride, rows, F, w, w_stride, per > 0 ? per : 1);
+                       src_stride, (__nv_bfloat16*)dst, dst_stride, rows, F, w, w_stride, per > 0 ? per : 1, act, mult);
   }
 #define LAUNCH(TI, TO)                                                                                  \
   return sglc_launch(gated_act_kernel<TI, TO>, dim3(blocks), dim3(256), 0, stream, 1, true, (const TI*)src, \
-                     src_stride, (TO*)dst, dst_stride, rows, F, w, w_stride, per > 0 ? per : 1)
+                     src_stride, (TO*)dst, dst_stride, rows, F, w, w_stride, per > 0 ? per : 1, act, mult)
   if (src_dtype == SGLC_F32 && dst_dtype == SGLC_F32) LAUNCH(float, float);
   if (src_dtype == SGLC_F32 && dst_dtype == SGLC_BF16) LAUNCH(float, __nv_bfloat16);
   if (src_dtype == SGLC_BF16 && dst_dtype == SGLC_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
 #undef LAUNCH
+  return SGLC_ERR_ARGUMENT;
+}
+
+SGLC_API int sglc_gated_act(const void* src, long long src_stride, int src_dtype, void* dst, long long dst_stride,
+                            int dst_dtype, int rows, int F, const float* w, long long w_stride, int per,
+                            cudaStream_t stream) {
+  return sglc_gated_act_ext(src, src_stride, src_dtype, dst, dst_stride, dst_dtype, rows, F, w, w_stride, per, GA_SILU,
+                            1.0f, stream);
+}
+
+// 32-bit rows into a column range of rows of another precision: dst[r][j] = src[r][j], j < cols
+// (the operand of a product made of several streams laid side by side).
+template <typename TO>
+__global__ void cast_rows_kernel(const float* __restrict__ src, long long src_stride, TO* __restrict__ dst,
+                                 long long dst_stride, int rows, int cols) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long total = (long long)rows * cols;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / cols, c = i % cols;
+    dst[r * dst_stride + c] = from_f32<TO>(src[r * src_stride + c]);
+  }
+}
+
+SGLC_API int sglc_cast_rows(const float* src, long long src_stride, void* dst, long long dst_stride, int dst_dtype,
+                            int rows, int cols, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return SGLC_OK;
+  const long long total = (long long)rows * cols;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dst_dtype == SGLC_F32)
+    return sglc_launch(cast_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1, true, src, src_stride,
+                       (float*)dst, dst_stride, rows, cols);
+  if (dst_dtype == SGLC_BF16)
+    return sglc_launch(cast_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, 1, true, src, src_stride,
+                       (__nv_bfloat16*)dst, dst_stride, rows, cols);
   return SGLC_ERR_ARGUMENT;
 }

@@ -2,13 +2,13 @@
 // head's read-out, or all heads' side by side) is divided by its root mean square,
 //   y = o / sqrt(mean(o^2) + eps) * gain * act(gate),
 // with a gain of `width` entries that every row of a token shares and a gate of the row's shape
-// taken through silu or a sigmoid.  Statistics and the gate are 32-bit; the result is written in
+// taken through silu or a sigmoid (or no gate: the norm alone).  Statistics and the gate are 32-bit; the result is written in
 // the precision of the product that follows.  A warp a row.
 #include "common.cuh"
 
 SGLC_DEFINE_ERROR_STRING()
 
-enum { GN_SILU = 0, GN_SIGMOID = 1 };
+enum { GN_SILU = 0, GN_SIGMOID = 1, GN_NONE = 2 };   // GN_NONE: no gate at all (gate may be null)
 
 template <typename TO>
 __global__ void __launch_bounds__(128)
@@ -23,13 +23,17 @@ gated_norm_kernel(const float* __restrict__ o, long long o_stride, const float* 
   const long long t = row / groups;
   const int c0 = (int)(row % groups) * width;
   const float* op = o + t * o_stride + c0;
-  const float* gp = gate + t * gate_stride + c0;
+  const float* gp = act == GN_NONE ? nullptr : gate + t * gate_stride + c0;
   float ss = 0.0f;
   for (int d = lane; d < width; d += 32) ss = fmaf(op[d], op[d], ss);
   ss = warp_sum(ss);
   const float inv = 1.0f / sqrtf(ss / (float)width + eps);
   TO* yp = y + t * y_stride + c0;
   for (int d = lane; d < width; d += 32) {
+    if (act == GN_NONE) {
+      yp[d] = from_f32<TO>(op[d] * inv * gain[d]);
+      continue;
+    }
     const float g = gp[d];
     const float s = 1.0f / (1.0f + expf(-g));
     yp[d] = from_f32<TO>(op[d] * inv * gain[d] * (act == GN_SILU ? g * s : s));
@@ -41,7 +45,7 @@ SGLC_API int sglc_gated_norm(const float* o, long long o_stride, const float* ga
                              const float* gain, void* y, long long y_stride, int y_dtype, int T, int groups,
                              int width, float eps, int act, cudaStream_t stream) {
   if (T <= 0) return SGLC_OK;
-  if (groups <= 0 || width <= 0 || (act != GN_SILU && act != GN_SIGMOID)) return SGLC_ERR_ARGUMENT;
+  if (groups <= 0 || width <= 0 || act < GN_SILU || act > GN_NONE || (act != GN_NONE && !gate)) return SGLC_ERR_ARGUMENT;
   const long long n_rows = (long long)T * groups;
   const dim3 grid((unsigned)((n_rows + 3) / 4));
   if (y_dtype == SGLC_F32)

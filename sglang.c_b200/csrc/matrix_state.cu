@@ -5,6 +5,10 @@
 //       S <- d_h S + k_t v_t^T                         o_t = S^T q_t
 //   gated delta rule (per token a decay g_t and a step size b_t, both per head):
 //       S <- g_t S;  u = b_t (v_t - S^T k_t);  S <- S + k_t u^T;   o_t = S^T q_t
+//   row-gated form (HGRN2: the forget gate of a row also says how much of the value it takes in):
+//       f_t = l + (1 - l) sigmoid(x_t)  per head and row, l a learned lower bound in [0, 1);
+//       S <- diag(f_t) S + (1 - f_t) v_t^T              o_t = S^T q_t
+//     (x_t arrives where the other forms take k_t; the kernel makes f_t as it stages the token)
 // in this order: the read-out sees the current token's write.
 //
 // Column j of S needs nothing of the other columns: S^T k, the update and S^T q are, per column,
@@ -18,7 +22,7 @@
 // instructions in all; key sizes of 33..64 take PER = 8 in steps with few (request, head) pairs,
 // where it was a tenth faster.
 // q and k may have fewer heads than v (head h reads q/k head h / (H / G)).
-// With `silu_in` the kernel applies silu to q, k and v as it stages them.
+// With `silu_in` the kernel applies silu to q, k and v as it stages them (row-gated form: to q only).
 #include "common.cuh"
 
 SGLC_DEFINE_ERROR_STRING()
@@ -26,7 +30,7 @@ SGLC_DEFINE_ERROR_STRING()
 constexpr int MS_UNROLL = 4;      // tokens worked on without a loop between them
 constexpr int MS_MAX_DIM = 256;   // key sizes up to 16 entries a lane x 16 lanes
 
-enum { MS_DECAY = 0, MS_DELTA = 1 };
+enum { MS_DECAY = 0, MS_DELTA = 1, MS_ROWGATE = 2 };
 
 struct MsArgs {
   const float* q; long long q_stride;     // [T][..], head g at columns g*D
@@ -34,6 +38,7 @@ struct MsArgs {
   const float* v; long long v_stride;     // head h at columns h*V
   const float* gates; long long gates_stride;   // delta: [T][2H] beta then decay
   const float* head_decay;                // decay form: [H]
+  const float* lower;                     // row-gated form: [H*D] lower bounds of the forget gates
   float* out; long long out_stride;       // [T][H*V]
   float* state;                           // [n_slots][H][D][V]
   const int* q_start; const int* state_slots;
@@ -112,14 +117,20 @@ matrix_state_kernel(MsArgs p) {
       const int x = tid + n * THREADS;
       if (x < MS_BATCH * DP) {
         const int b = x / DP, i = x % DP, at = b * SP + i / MS_PER * LP + i % MS_PER;
-        ks[buf][at] = p.silu_in ? ms_silu(rk[n]) : rk[n];
+        if (MODE == MS_ROWGATE) {
+          // (rows beyond the key size keep a gate of one: their entries stay zero)
+          const float lo = i < p.D ? __ldg(p.lower + (size_t)g * p.D + i) : 1.0f;
+          ks[buf][at] = lo + (1.0f - lo) * (1.0f / (1.0f + expf(-rk[n])));
+        } else {
+          ks[buf][at] = p.silu_in ? ms_silu(rk[n]) : rk[n];
+        }
         qs[buf][at] = p.silu_in ? ms_silu(rq[n]) : rq[n];
       }
     }
 #pragma unroll
     for (int n = 0; n < NV; n++) {
       const int x = tid + n * THREADS;
-      if (x < MS_BATCH * COLS) vs[buf][x] = p.silu_in ? ms_silu(rv[n]) : rv[n];
+      if (x < MS_BATCH * COLS) vs[buf][x] = (p.silu_in && MODE != MS_ROWGATE) ? ms_silu(rv[n]) : rv[n];
     }
     if (MODE == MS_DELTA) {
 #pragma unroll
@@ -169,6 +180,18 @@ matrix_state_kernel(MsArgs p) {
           S[e + 1] = fmaf(kk[e + 1], u, gd * S[e + 1]);
           S[e + 2] = fmaf(kk[e + 2], u, gd * S[e + 2]);
           S[e + 3] = fmaf(kk[e + 3], u, gd * S[e + 3]);
+          o0 = fmaf(S[e], qq[e], o0);
+          o1 = fmaf(S[e + 1], qq[e + 1], o1);
+          o2 = fmaf(S[e + 2], qq[e + 2], o2);
+          o3 = fmaf(S[e + 3], qq[e + 3], o3);
+        }
+      } else if (MODE == MS_ROWGATE) {
+#pragma unroll
+        for (int e = 0; e < MS_PER; e += 4) {
+          S[e] = fmaf(kk[e], S[e], (1.0f - kk[e]) * vv);
+          S[e + 1] = fmaf(kk[e + 1], S[e + 1], (1.0f - kk[e + 1]) * vv);
+          S[e + 2] = fmaf(kk[e + 2], S[e + 2], (1.0f - kk[e + 2]) * vv);
+          S[e + 3] = fmaf(kk[e + 3], S[e + 3], (1.0f - kk[e + 3]) * vv);
           o0 = fmaf(S[e], qq[e], o0);
           o1 = fmaf(S[e + 1], qq[e + 1], o1);
           o2 = fmaf(S[e + 2], qq[e + 2], o2);
@@ -247,17 +270,18 @@ SGLC_API void sglc_matrix_state_set_per(int per) { g_ms_per = per; }
 
 // mode 0: decay form (head_decay [H]); mode 1: gated delta rule (gates [T][2H]: beta, decay).
 // q, k: float rows with G heads of D; v: H heads of V; out: [T][H*V] float; state [n_slots][H][D][V].
-SGLC_API int sglc_matrix_state(int mode, const float* q, long long q_stride, const float* k, long long k_stride,
-                               const float* v, long long v_stride, const float* gates, long long gates_stride,
-                               const float* head_decay, float* out, long long out_stride, float* state,
-                               int n_slots, const int* q_start, const int* state_slots, int R, int H, int G,
-                               int D, int V, int silu_in, int* err, cudaStream_t stream) {
+// mode 2: row-gated form (k holds the gates' pre-activations, lower [H*D] their lower bounds; G == H).
+SGLC_API int sglc_matrix_state_ext(int mode, const float* q, long long q_stride, const float* k, long long k_stride,
+                                   const float* v, long long v_stride, const float* gates, long long gates_stride,
+                                   const float* head_decay, const float* lower, float* out, long long out_stride,
+                                   float* state, int n_slots, const int* q_start, const int* state_slots, int R, int H,
+                                   int G, int D, int V, int silu_in, int* err, cudaStream_t stream) {
   if (R <= 0) return SGLC_OK;
   if (H <= 0 || G <= 0 || H % G != 0 || D <= 0 || V <= 0) return SGLC_ERR_ARGUMENT;
   if (D > MS_MAX_DIM || H > 65535) return SGLC_ERR_UNSUPPORTED;
   MsArgs p = {};
   p.q = q; p.q_stride = q_stride; p.k = k; p.k_stride = k_stride; p.v = v; p.v_stride = v_stride;
-  p.gates = gates; p.gates_stride = gates_stride; p.head_decay = head_decay;
+  p.gates = gates; p.gates_stride = gates_stride; p.head_decay = head_decay; p.lower = lower;
   p.out = out; p.out_stride = out_stride; p.state = state; p.q_start = q_start; p.state_slots = state_slots;
   p.R = R; p.H = H; p.G = G; p.D = D; p.V = V; p.n_slots = n_slots; p.silu_in = silu_in; p.err = err;
   // Entries a lane keeps: 8 for key sizes of 33..64 while the warps still find a scheduler each (two
@@ -289,5 +313,19 @@ SGLC_API int sglc_matrix_state(int mode, const float* q, long long q_stride, con
     if (!gates) return SGLC_ERR_ARGUMENT;
     MS_GO(MS_DELTA);
   }
+  if (mode == MS_ROWGATE) {
+    if (!lower || G != H) return SGLC_ERR_ARGUMENT;
+    MS_GO(MS_ROWGATE);
+  }
   return SGLC_ERR_ARGUMENT;
+}
+
+SGLC_API int sglc_matrix_state(int mode, const float* q, long long q_stride, const float* k, long long k_stride,
+                               const float* v, long long v_stride, const float* gates, long long gates_stride,
+                               const float* head_decay, float* out, long long out_stride, float* state,
+                               int n_slots, const int* q_start, const int* state_slots, int R, int H, int G,
+                               int D, int V, int silu_in, int* err, cudaStream_t stream) {
+  if (mode == MS_ROWGATE) return SGLC_ERR_ARGUMENT;
+  return sglc_matrix_state_ext(mode, q, q_stride, k, k_stride, v, v_stride, gates, gates_stride, head_decay, nullptr, out,
+                               out_stride, state, n_slots, q_start, state_slots, R, H, G, D, V, silu_in, err, stream);
 }

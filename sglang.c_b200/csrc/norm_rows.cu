@@ -8,6 +8,8 @@
 //   scatter   dst[dst_rows[r], :] = y            (the rows of a paged cache, by slot)
 //   add       dst[r, :] += y                     (float: a norm behind a sublayer, summed into the
 //                                                 32-bit residual stream)
+// In groups: a row is split into `groups` equal consecutive parts, each normalised by its own
+// statistics; gain and bias span the whole row.  A block then takes one part of one row.
 // One block a row; the order of a row's additions depends on the row's width only, so a row's
 // bits do not depend on what else is in the step.
 #include "common.cuh"
@@ -55,14 +57,17 @@ __global__ void norm_rows_kernel(const TI* __restrict__ src, long long src_strid
                                  const int* __restrict__ src_rows, const float* __restrict__ gain, const float* __restrict__ bias,
                                  TO* __restrict__ dst, long long dst_stride, const int* __restrict__ dst_rows,
                                  int n_rows, int E, float eps, int form, long long dst_row_limit,
-                                 int* __restrict__ err) {
+                                 int* __restrict__ err, int groups) {
   extern __shared__ __align__(16) float srow[];   // E floats
   __shared__ float red[33];
-  const int r = blockIdx.x;
+  // (groups > 1: a block takes one of a row's equal consecutive parts, E being the part's width)
+  const int r = blockIdx.x / groups, part = (blockIdx.x % groups) * E;
   if (r >= n_rows) return;
+  if (gain) gain += part;
+  if (bias) bias += part;
   pdl_launch_dependents();
   pdl_wait();
-  const TI* xr = src + (size_t)(src_rows ? src_rows[r] : r) * src_stride;
+  const TI* xr = src + (size_t)(src_rows ? src_rows[r] : r) * src_stride + part;
   float s = 0.0f;
   if constexpr (VEC) {
     for (int i = threadIdx.x; i < E / 4; i += blockDim.x) {
@@ -95,7 +100,7 @@ __global__ void norm_rows_kernel(const TI* __restrict__ src, long long src_strid
     row = dst_rows[r];
     if (row < 0 || !sglc_index_ok(row, dst_row_limit, err)) return;
   }
-  TO* o = dst + (size_t)row * dst_stride;
+  TO* o = dst + (size_t)row * dst_stride + part;
   if constexpr (VEC) {
     for (int i = threadIdx.x; i < E / 4; i += blockDim.x) {
       float4 y = norm4(reinterpret_cast<const float4*>(srow)[i], mean, inv, gain, bias, i);
@@ -268,13 +273,15 @@ SGLC_API int sglc_norm_add_tail(const float* y, long long y_stride, const float*
 // form: 0 layer, 1 RMS.  src_rows: null, or the source row of every output row (a gather).  src_dtype/dst_dtype: SGLC_F32 or SGLC_BF16.  dst_rows: null, or the
 // destination row of every source row (negative: the row is skipped); dst_row_limit: rows the
 // destination holds (the bounds-check build compares).  add != 0: dst (float) += y.
-SGLC_API int sglc_norm_rows(const void* src, long long src_stride, int src_dtype, const int* src_rows,
-                            const float* gain,
-                            const float* bias, void* dst, long long dst_stride, int dst_dtype,
-                            const int* dst_rows, long long dst_row_limit, int n_rows, int E, float eps,
-                            int form, int add, int* err, cudaStream_t stream) {
+SGLC_API int sglc_norm_rows_grouped(const void* src, long long src_stride, int src_dtype, const int* src_rows,
+                                    const float* gain,
+                                    const float* bias, void* dst, long long dst_stride, int dst_dtype,
+                                    const int* dst_rows, long long dst_row_limit, int n_rows, int E_row, float eps,
+                                    int form, int add, int groups, int* err, cudaStream_t stream) {
   if (n_rows <= 0) return SGLC_OK;
-  if (E <= 0 || (form != NORM_LAYER && form != NORM_RMS)) return SGLC_ERR_ARGUMENT;
+  if (E_row <= 0 || groups <= 0 || E_row % groups != 0 || (form != NORM_LAYER && form != NORM_RMS)) return SGLC_ERR_ARGUMENT;
+  if ((long long)n_rows * groups > 0x7fffffffLL) return SGLC_ERR_UNSUPPORTED;
+  const int E = E_row / groups;            // what a block normalises
   if (add && dst_dtype != SGLC_F32) return SGLC_ERR_ARGUMENT;
   const size_t smem = (size_t)E * sizeof(float);
   if (smem > 200 * 1024) return SGLC_ERR_UNSUPPORTED;
@@ -292,9 +299,9 @@ SGLC_API int sglc_norm_rows(const void* src, long long src_stride, int src_dtype
     if (smem > 48 * 1024)                                                                            \
       cudaFuncSetAttribute(norm_rows_kernel<TI, TO, ADD, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                            (int)smem);                                                               \
-    return sglc_launch(norm_rows_kernel<TI, TO, ADD, VEC>, dim3(n_rows), dim3(threads), smem, stream, 1,   \
+    return sglc_launch(norm_rows_kernel<TI, TO, ADD, VEC>, dim3(n_rows * groups), dim3(threads), smem, stream, 1, \
                        true, (const TI*)src, src_stride, src_rows, gain, bias, (TO*)dst, dst_stride, dst_rows,  \
-                       n_rows, E, eps, form, dst_row_limit, err);                                     \
+                       n_rows, E, eps, form, dst_row_limit, err, groups);                             \
   } while (0)
   if (src_dtype == SGLC_F32) {
     if (add) LAUNCH(float, float, true);
@@ -308,4 +315,13 @@ SGLC_API int sglc_norm_rows(const void* src, long long src_stride, int src_dtype
 #undef LAUNCH
 #undef LAUNCH_V
   return SGLC_ERR_ARGUMENT;
+}
+
+SGLC_API int sglc_norm_rows(const void* src, long long src_stride, int src_dtype, const int* src_rows,
+                            const float* gain,
+                            const float* bias, void* dst, long long dst_stride, int dst_dtype,
+                            const int* dst_rows, long long dst_row_limit, int n_rows, int E, float eps,
+                            int form, int add, int* err, cudaStream_t stream) {
+  return sglc_norm_rows_grouped(src, src_stride, src_dtype, src_rows, gain, bias, dst, dst_stride, dst_dtype, dst_rows,
+                                dst_row_limit, n_rows, E, eps, form, add, 1, err, stream);
 }

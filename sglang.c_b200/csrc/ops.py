@@ -680,9 +680,11 @@ def sample(logits, params, hist_tok, hist_cnt, out_tok, out_logprob=None):
 NORM_FORMS = {"layer": 0, "rms": 1}
 
 
-def norm_rows(src, gain, bias, eps, dst, form="layer", add=False, dst_rows=None, src_rows=None):
+def norm_rows(src, gain, bias, eps, dst, form="layer", add=False, dst_rows=None, src_rows=None, groups=1):
     """dst[r,:] = norm(src[r,:]) * gain + bias (gain, bias: float32 vectors or None), `form`
     "layer" (mean removed) or "rms"; src float32 or bfloat16 [n,E] with a free row stride.
+    groups > 1: a row is `groups` equal consecutive parts, each normalised by its own statistics
+    (gain and bias still span the row).
     add=True: dst (float32) += the normalised rows.  dst_rows (int32 [n]): row r goes to
     dst[dst_rows[r], :] (dst [rows, E]: the rows of a paged cache seen flat).  src_rows (int32):
     output row r is made from src[src_rows[r], :]; as many rows as dst has (or dst_rows names)."""
@@ -706,12 +708,15 @@ def norm_rows(src, gain, bias, eps, dst, form="layer", add=False, dst_rows=None,
         raise KernelError("norm_rows: fewer destination rows than source rows")
     if add and dst.dtype != torch.float32:
         raise KernelError("norm_rows: the sum goes into a float32 destination")
+    if groups < 1 or E % groups:
+        raise KernelError(f"norm_rows: a row of {E} does not split into {groups} equal parts")
     lib = build.load("norm_rows")
-    code = lib.sglc_norm_rows(_ptr(src), ctypes.c_longlong(src.stride(0)), _dt(src, "norm source"), _ptr(src_rows),
-                              _ptr(gain),
-                              _ptr(bias), _ptr(dst), ctypes.c_longlong(dst.stride(0)), _dt(dst, "norm destination"),
-                              _ptr(dst_rows), ctypes.c_longlong(dst.shape[0]), n, E, ctypes.c_float(eps),
-                              NORM_FORMS[form], 1 if add else 0, _ptr(tc_error_flag(src.device)), _stream())
+    code = lib.sglc_norm_rows_grouped(_ptr(src), ctypes.c_longlong(src.stride(0)), _dt(src, "norm source"),
+                                      _ptr(src_rows), _ptr(gain),
+                                      _ptr(bias), _ptr(dst), ctypes.c_longlong(dst.stride(0)),
+                                      _dt(dst, "norm destination"), _ptr(dst_rows), ctypes.c_longlong(dst.shape[0]), n,
+                                      E, ctypes.c_float(eps), NORM_FORMS[form], 1 if add else 0, int(groups),
+                                      _ptr(tc_error_flag(src.device)), _stream())
     _check(lib, code, f"norm_rows (width {E})")
 
 
@@ -869,13 +874,15 @@ MATRIX_STATE_MAX_DIM = 256
 
 
 def matrix_state(mode, q, k, v, out, state, q_start, state_slots, n_requests, n_heads, n_qk_heads, dim, v_dim,
-                 gates=None, head_decay=None, silu_in=False):
+                 gates=None, head_decay=None, silu_in=False, lower=None):
     """A recurrence with a matrix state per head over the step's tokens (see matrix_state.cu).
     mode "decay": S <- d_h S + k v^T (head_decay float32 [H]); mode "delta": the gated delta rule
-    (gates float32 [T, 2H]: beta, then decay).  o = S^T q after the token's write.  q, k: float32
+    (gates float32 [T, 2H]: beta, then decay); mode "row_gate": S <- diag(f) S + (1 - f) v^T with
+    f = lower + (1 - lower) sigmoid(k) per head and row (k holds the gates' pre-activations, lower
+    float32 [H*dim]; silu_in then acts on q only).  o = S^T q after the token's write.  q, k: float32
     [T, n_qk_heads*dim]; v: float32 [T, n_heads*v_dim]; out float32 [T, n_heads*v_dim]; state float32
     [n_slots, n_heads, dim, v_dim], read and written in place for the requests' slots."""
-    _need_cuda(q, k, v, out, state, q_start, state_slots, gates, head_decay)
+    _need_cuda(q, k, v, out, state, q_start, state_slots, gates, head_decay, lower)
     T = out.shape[0]
     _f32_rows(q, "matrix_state: q", n_qk_heads * dim)
     _f32_rows(k, "matrix_state: k", n_qk_heads * dim)
@@ -887,7 +894,11 @@ def matrix_state(mode, q, k, v, out, state, q_start, state_slots, n_requests, n_
         raise KernelError(f"matrix_state: key size {dim} is beyond the kernel's {MATRIX_STATE_MAX_DIM}")
     _i32(q_start, "q_start")
     _i32(state_slots, "state_slots")
-    m = {"decay": 0, "delta": 1}[mode]
+    m = {"decay": 0, "delta": 1, "row_gate": 2}[mode]
+    if m == 2 and (lower is None or lower.dtype != torch.float32 or lower.numel() != n_heads * dim
+                   or not lower.is_contiguous() or n_qk_heads != n_heads):
+        raise KernelError("matrix_state: the row-gated form takes one float32 lower bound per head and row, "
+                          "and as many gate heads as value heads")
     if m == 0 and (head_decay is None or head_decay.dtype != torch.float32 or head_decay.numel() != n_heads):
         raise KernelError("matrix_state: the decay form takes one float32 decay per head")
     if m == 1:
@@ -895,10 +906,10 @@ def matrix_state(mode, q, k, v, out, state, q_start, state_slots, n_requests, n_
             raise KernelError("matrix_state: the delta rule takes its gates")
         _f32_rows(gates, "matrix_state: gates", 2 * n_heads)
     lib = build.load("matrix_state")
-    code = lib.sglc_matrix_state(m, _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(k), ctypes.c_longlong(k.stride(0)),
+    code = lib.sglc_matrix_state_ext(m, _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(k), ctypes.c_longlong(k.stride(0)),
                                  _ptr(v), ctypes.c_longlong(v.stride(0)), _ptr(gates),
                                  ctypes.c_longlong(gates.stride(0) if gates is not None else 0), _ptr(head_decay),
-                                 _ptr(out), ctypes.c_longlong(out.stride(0)), _ptr(state), state.shape[0],
+                                 _ptr(lower), _ptr(out), ctypes.c_longlong(out.stride(0)), _ptr(state), state.shape[0],
                                  _ptr(q_start), _ptr(state_slots), int(n_requests), int(n_heads), int(n_qk_heads),
                                  int(dim), int(v_dim), 1 if silu_in else 0, _ptr(tc_error_flag(q.device)), _stream())
     _check(lib, code, f"matrix_state ({mode}, {dim} x {v_dim})")
@@ -906,20 +917,26 @@ def matrix_state(mode, q, k, v, out, state, q_start, state_slots, n_requests, n_
 
 def gated_norm(o, gate, gain, y, groups, width, eps, act):
     """y = o / sqrt(mean(o^2) + eps) * gain * act(gate) per row of `width` (a token has `groups`
-    rows side by side; gain float32 [width] serves them all); act "silu" or "sigmoid".  o, gate:
-    float32 [T, groups*width]; y: float32 or bfloat16."""
+    rows side by side; gain float32 [width] serves them all); act "silu" or "sigmoid", or "none"
+    with gate None: the norm alone.  o, gate: float32 [T, groups*width]; y: float32 or bfloat16."""
     _need_cuda(o, gate, gain, y)
     T = y.shape[0]
     _f32_rows(o, "gated_norm: o", groups * width)
-    _f32_rows(gate, "gated_norm: gate", groups * width)
+    if (act == "none") != (gate is None):
+        raise KernelError("gated_norm: a gate goes with silu or sigmoid, none with \"none\"")
+    if gate is not None:
+        _f32_rows(gate, "gated_norm: gate", groups * width)
     if gain.dtype != torch.float32 or gain.numel() != width or not gain.is_contiguous():
         raise KernelError("gated_norm: the gain is a float32 vector of the row width")
-    if tuple(y.shape) != (T, groups * width) or y.stride(1) != 1 or o.shape[0] < T or gate.shape[0] < T:
+    if tuple(y.shape) != (T, groups * width) or y.stride(1) != 1 or o.shape[0] < T \
+            or (gate is not None and gate.shape[0] < T):
         raise KernelError("gated_norm: y is [T, groups*width]")
     lib = build.load("gated_norm")
-    code = lib.sglc_gated_norm(_ptr(o), ctypes.c_longlong(o.stride(0)), _ptr(gate), ctypes.c_longlong(gate.stride(0)),
+    code = lib.sglc_gated_norm(_ptr(o), ctypes.c_longlong(o.stride(0)), _ptr(gate),
+                               ctypes.c_longlong(gate.stride(0) if gate is not None else 0),
                                _ptr(gain), _ptr(y), ctypes.c_longlong(y.stride(0)), _dt(y, "gated_norm output"), T,
-                               int(groups), int(width), ctypes.c_float(eps), {"silu": 0, "sigmoid": 1}[act], _stream())
+                               int(groups), int(width), ctypes.c_float(eps), {"silu": 0, "sigmoid": 1, "none": 2}[act],
+                               _stream())
     _check(lib, code, f"gated_norm (width {width})")
 
 
@@ -978,9 +995,13 @@ def attention_ext(q, cache, block_table, token_req, positions, out, n_heads, n_k
     _check(lib, code, f"attention_ext (head {dim}/{v_dim}, up to {max_keys} keys)")
 
 
-def gated_act(src, dst, weights=None, per=0):
-    """dst[r, j] = silu(src[r, j]) * src[r, F + j] (* weights[r, j // per]); src [rows, 2F] holds the
-    gate columns, then the up columns; weights: float32 [rows, F // per] or None."""
+GATE_ACTS = {"silu": 0, "gelu_tanh": 1}
+
+
+def gated_act(src, dst, weights=None, per=0, act="silu", mult=1.0):
+    """dst[r, j] = act(src[r, j]) * src[r, F + j] (* weights[r, j // per]) * mult; src [rows, 2F] holds
+    the gate columns, then the up columns; weights: float32 [rows, F // per] or None; act "silu" or
+    "gelu_tanh"; mult: one more factor of every result, taken in 32-bit."""
     _need_cuda(src, dst, weights)
     rows, F = dst.shape
     if src.shape[1] != 2 * F or src.shape[0] < rows or src.stride(1) != 1 or dst.stride(1) != 1:
@@ -990,10 +1011,10 @@ def gated_act(src, dst, weights=None, per=0):
         if per <= 0 or F % per or weights.shape[1] != F // per or weights.shape[0] < rows:
             raise KernelError("gated_act: one weight per row and block of `per` columns")
     lib = build.load("elementwise")
-    code = lib.sglc_gated_act(_ptr(src), ctypes.c_longlong(src.stride(0)), _dt(src, "gated_act source"), _ptr(dst),
-                              ctypes.c_longlong(dst.stride(0)), _dt(dst, "gated_act destination"), rows, F,
-                              _ptr(weights), ctypes.c_longlong(weights.stride(0) if weights is not None else 0),
-                              int(per), _stream())
+    code = lib.sglc_gated_act_ext(_ptr(src), ctypes.c_longlong(src.stride(0)), _dt(src, "gated_act source"), _ptr(dst),
+                                  ctypes.c_longlong(dst.stride(0)), _dt(dst, "gated_act destination"), rows, F,
+                                  _ptr(weights), ctypes.c_longlong(weights.stride(0) if weights is not None else 0),
+                                  int(per), GATE_ACTS[act], ctypes.c_float(mult), _stream())
     _check(lib, code, "gated_act")
 
 
@@ -1018,3 +1039,122 @@ def router(logits, correction, dense, ids, weights, top, n_groups=1, keep=1, ren
                            ctypes.c_longlong(dense.stride(0)), _ptr(ids), _ptr(weights), T, E, int(top), int(n_groups),
                            int(keep), 1 if renorm else 0, ctypes.c_float(weight_scale), _stream())
     _check(lib, code, f"router ({E} experts, {top} chosen)")
+
+
+def cast_rows(src, dst):
+    """dst[r, j] = src[r, j] for the columns dst has: float32 rows into rows (a column range of
+    wider rows, if dst is such a view) of float32 or bfloat16."""
+    _need_cuda(src, dst)
+    rows, cols = dst.shape
+    _f32_rows(src, "cast_rows: src")
+    if src.shape[0] < rows or src.shape[1] < cols or dst.stride(1) != 1:
+        raise KernelError("cast_rows: src float32 [>= rows, >= cols]; dst rows contiguous")
+    lib = build.load("elementwise")
+    code = lib.sglc_cast_rows(_ptr(src), ctypes.c_longlong(src.stride(0)), _ptr(dst), ctypes.c_longlong(dst.stride(0)),
+                              _dt(dst, "cast_rows destination"), rows, cols, _stream())
+    _check(lib, code, "cast_rows")
+
+
+ROTARY_PAIRINGS = {"halves": 0, "neighbours": 1}
+
+
+def latent_rope(qx, low, gain, eps, positions, freq, mult, dims, pairing, q_out, rows, slots, n_heads, rank, rot_dim):
+    """The input stage of a latent attention with a turned part (see rotary.cu).  qx: float32
+    [T, H*(rank+rot_dim)], every head [rank entries that pass | rot_dim entries turned by position];
+    low: float32 [T, rank+rot_dim] or None, the token's latent (its first `rank` entries divided by
+    their root mean square, times gain) and one shared key part (turned), written to `rows`
+    [n_rows, rank+rot_dim] at slots; q_out [T, H*(rank+rot_dim)] in the cache's precision.  Of the
+    rot_dim entries the first `dims` are turned: pairs (i, i + dims/2) ("halves") or (2i, 2i+1)
+    ("neighbours"); freq float64 [dims/2]."""
+    _need_cuda(qx, low, gain, positions, freq, q_out, rows, slots)
+    T = q_out.shape[0]
+    W = rank + rot_dim
+    _f32_rows(qx, "latent_rope: qx", n_heads * W)
+    _i32(positions, "positions")
+    if freq.dtype != torch.float64 or freq.numel() != dims // 2 or not freq.is_contiguous():
+        raise KernelError("latent_rope: one float64 frequency per turned pair")
+    if tuple(q_out.shape) != (T, n_heads * W) or q_out.stride(1) != 1:
+        raise KernelError("latent_rope: queries leave as [T, heads*(rank+rot_dim)]")
+    n_rows = 0
+    if low is not None:
+        _f32_rows(low, "latent_rope: low", W)
+        _i32(slots, "slots")
+        if gain.dtype != torch.float32 or gain.numel() != rank or rows.dim() != 2 or rows.shape[1] != W \
+                or not rows.is_contiguous() or rows.dtype != q_out.dtype:
+            raise KernelError("latent_rope: gain float32 [rank]; cache rows [n, rank+rot_dim] of the queries' dtype")
+        n_rows = rows.shape[0]
+    lib = build.load("rotary")
+    code = lib.sglc_latent_rope(_ptr(qx), ctypes.c_longlong(qx.stride(0)), _ptr(low),
+                                ctypes.c_longlong(low.stride(0) if low is not None else 0), _ptr(gain),
+                                ctypes.c_float(eps), _ptr(positions), _ptr(freq), ctypes.c_float(mult), int(dims),
+                                ROTARY_PAIRINGS[pairing], _ptr(q_out), ctypes.c_longlong(q_out.stride(0)),
+                                _ptr(rows if low is not None else None), _ptr(slots if low is not None else None),
+                                ctypes.c_longlong(n_rows), T, int(n_heads), int(rank), int(rot_dim),
+                                _dt(q_out, "latent_rope queries"), _ptr(tc_error_flag(qx.device)), _stream())
+    _check(lib, code, f"latent_rope (rank {rank}, turned {rot_dim})")
+
+
+TALK_MAX_HEADS, TALK_MAX_DIM = 32, 256
+
+
+def talk_prep(x, wq, wk, eps, q_out, cache, slots, n_heads, n_kv_heads, dim, page_size):
+    """The input stage of a talking-heads attention (see attention_talk.cu).  x: float32 [T, >=
+    (H+G)*dim], queries then keys as projected; wq, wk: float32 [dim], the gains of the queries'
+    and keys' norms; q_out: float32 [T, H*dim], the normalised queries times both gains; the keys
+    go as they are into cache [n_pages, 1, G, page_size, dim] at slots."""
+    _need_cuda(x, wq, wk, q_out, cache, slots)
+    T = q_out.shape[0]
+    _f32_rows(x, "talk_prep: x")
+    _f32_rows(q_out, "talk_prep: q_out", n_heads * dim)
+    _i32(slots, "slots")
+    n_pages = cache.shape[0]
+    if x.shape[1] < (n_heads + n_kv_heads) * dim or x.shape[0] < T or not cache.is_contiguous() \
+            or cache.numel() != n_pages * n_kv_heads * page_size * dim:
+        raise KernelError(f"talk_prep: x holds queries and keys; cache {tuple(cache.shape)} keeps one row per "
+                          f"position and each of {n_kv_heads} heads of {dim}")
+    for v in (wq, wk):
+        if v.dtype != torch.float32 or v.numel() != dim or not v.is_contiguous():
+            raise KernelError("talk_prep: the norms' gains are float32 [dim]")
+    lib = build.load("attention_talk")
+    code = lib.sglc_talk_prep(_ptr(x), ctypes.c_longlong(x.stride(0)), _ptr(wq), _ptr(wk), ctypes.c_float(eps),
+                              _ptr(q_out), ctypes.c_longlong(q_out.stride(0)), _ptr(cache), _dt(cache, "cache"),
+                              _ptr(slots), T, int(n_heads), int(n_kv_heads), int(dim), int(page_size), n_pages,
+                              _ptr(tc_error_flag(x.device)), _stream())
+    _check(lib, code, f"talk_prep (head {dim})")
+
+
+def talk_attention(q, cache, block_table, token_req, positions, slopes, talk, gate, out, n_heads, n_kv_heads, dim,
+                   page_size, scale, eps, mult, window):
+    """Softmax attention with a distance penalty per head, the heads' weights mixed after the
+    softmax, values that are the cached keys, and a sigmoid output gate (see attention_talk.cu).
+    q: float32 [T, H*dim] from talk_prep; slopes float32 [H]; talk float32 [H, H]; gate: float32
+    rows [T, H*dim] or None; out [T, H*dim] of the cache's dtype; token_req None: token t is the
+    step's t-th request."""
+    _need_cuda(q, cache, block_table, token_req, positions, slopes, talk, gate, out)
+    T = out.shape[0]
+    _f32_rows(q, "talk_attention: q", n_heads * dim)
+    for t, nm in ((block_table, "block_table"), (positions, "positions")):
+        _i32(t, nm)
+    if token_req is not None:
+        _i32(token_req, "token_req")
+    if gate is not None:
+        _f32_rows(gate, "talk_attention: gate", n_heads * dim)
+    n_pages = cache.shape[0]
+    if slopes.dtype != torch.float32 or slopes.numel() != n_heads or talk.dtype != torch.float32 \
+            or talk.numel() != n_heads * n_heads or not talk.is_contiguous():
+        raise KernelError("talk_attention: slopes float32 [H], talk float32 [H, H]")
+    if tuple(out.shape) != (T, n_heads * dim) or out.stride(1) != 1 or out.dtype != cache.dtype \
+            or not cache.is_contiguous() or cache.numel() != n_pages * n_kv_heads * page_size * dim:
+        raise KernelError("talk_attention: out [T, H*dim] and the cache have one dtype")
+    if n_heads > TALK_MAX_HEADS or dim > TALK_MAX_DIM:
+        raise KernelError(f"talk_attention: up to {TALK_MAX_HEADS} heads of up to {TALK_MAX_DIM}")
+    lib = build.load("attention_talk")
+    code = lib.sglc_talk_attention(_ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(cache), _dt(cache, "cache"),
+                                   _ptr(block_table), block_table.stride(0), _ptr(token_req), _ptr(positions),
+                                   _ptr(slopes), _ptr(talk), _ptr(gate),
+                                   ctypes.c_longlong(gate.stride(0) if gate is not None else 0), _ptr(out),
+                                   ctypes.c_longlong(out.stride(0)), _dt(out, "talk_attention output"), T,
+                                   int(n_heads), int(n_kv_heads), int(dim), int(page_size), ctypes.c_float(scale),
+                                   ctypes.c_float(eps), ctypes.c_float(mult), int(window or 0), n_pages,
+                                   _ptr(tc_error_flag(q.device)), _stream())
+    _check(lib, code, f"talk_attention (head {dim}, {n_heads} heads)")

@@ -95,3 +95,80 @@ SGLC_API int sglc_rotary_kv(const float* x, long long x_stride, const int* posit
                        (__nv_bfloat16*)cache, slots, T, H, G, D, V, page_size, n_pages, err);
   return SGLC_ERR_ARGUMENT;
 }
+
+// The input stage of a latent attention with a turned part, in one launch, a block a token:
+//   every query head [R entries | Rd entries]: the first R pass (they are already in the latent's
+//     coordinates), the last Rd are turned by the token's position;
+//   the token's latent row `low` [R | Rd]: the first R are divided by their root mean square (eps
+//     inside the root) and multiplied by a gain, the last Rd (one key part that all heads share)
+//     are turned the same way; the row goes straight into the cache's rows at slots[t].
+// Of the Rd entries the first `dims` are turned, the rest pass.  `pairing` 0: pairs (i, i + dims/2);
+// 1: neighbours (2i, 2i + 1).  Angles as above: 64-bit, brought into one turn, then sincosf.
+// Queries arrive as 32-bit rows and leave in the activation precision, which is the cache's.
+template <typename TA>
+__global__ void __launch_bounds__(ROT_WARPS * 32)
+latent_rope_kernel(const float* __restrict__ qx, long long qx_stride, const float* __restrict__ low,
+                   long long low_stride, const float* __restrict__ gain, float eps, const int* __restrict__ positions,
+                   const double* __restrict__ freq, float mult, int dims, int pairing, TA* __restrict__ q_out,
+                   long long q_stride, TA* __restrict__ rows, const int* __restrict__ slots, long long n_rows, int T,
+                   int H, int R, int Rd, int* err) {
+  pdl_launch_dependents();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_wait();
+  const int pos = positions[t];
+  const int half = dims / 2, W = R + Rd;
+  for (int row = warp; row < H + (low ? 1 : 0); row += ROT_WARPS) {
+    const float* src;
+    TA* dst;
+    if (row < H) {
+      src = qx + (size_t)t * qx_stride + (size_t)row * W;
+      dst = q_out + (size_t)t * q_stride + (size_t)row * W;
+      for (int d = lane; d < R; d += 32) dst[d] = from_f32<TA>(src[d]);
+    } else {
+      const long long slot = slots[t];
+      if (slot < 0 || !sglc_index_ok(slot, n_rows, err)) continue;
+      src = low + (size_t)t * low_stride;
+      dst = rows + (size_t)slot * W;
+      float ss = 0.0f;
+      for (int d = lane; d < R; d += 32) ss = fmaf(src[d], src[d], ss);
+      ss = warp_sum(ss);
+      const float inv = 1.0f / sqrtf(ss / (float)R + eps);
+      for (int d = lane; d < R; d += 32) dst[d] = from_f32<TA>(src[d] * inv * gain[d]);
+    }
+    src += R;
+    dst += R;
+    for (int i = lane; i < half; i += 32) {
+      double a = (double)pos * freq[i];
+      a -= floor(a * 0.15915494309189535) * 6.283185307179586;
+      float sn, cs;
+      sincosf((float)a, &sn, &cs);
+      sn *= mult; cs *= mult;
+      const int iu = pairing ? 2 * i : i, iv = pairing ? 2 * i + 1 : i + half;
+      const float u = src[iu], v = src[iv];
+      dst[iu] = from_f32<TA>(u * cs - v * sn);
+      dst[iv] = from_f32<TA>(v * cs + u * sn);
+    }
+    for (int d = 2 * half + lane; d < Rd; d += 32) dst[d] = from_f32<TA>(src[d]);
+  }
+}
+
+// qx: float [T][H*(R+Rd)]; low: float [T][R+Rd] or null (a layer that reads latents another layer
+// cached); gain: float [R]; q_out: [T][H*(R+Rd)]; rows: the cache seen as [n_rows][R+Rd].
+SGLC_API int sglc_latent_rope(const float* qx, long long qx_stride, const float* low, long long low_stride,
+                              const float* gain, float eps, const int* positions, const double* freq, float mult,
+                              int dims, int pairing, void* q_out, long long q_stride, void* rows, const int* slots,
+                              long long n_rows, int T, int H, int R, int Rd, int dtype, int* err,
+                              cudaStream_t stream) {
+  if (T <= 0) return SGLC_OK;
+  if (H <= 0 || R <= 0 || Rd < 0 || dims < 0 || dims > Rd || dims % 2 != 0 || (low && (!gain || !rows || !slots)))
+    return SGLC_ERR_ARGUMENT;
+  if (dtype == SGLC_F32)
+    return sglc_launch(latent_rope_kernel<float>, dim3(T), dim3(ROT_WARPS * 32), 0, stream, 1, true, qx, qx_stride, low,
+                       low_stride, gain, eps, positions, freq, mult, dims, pairing, (float*)q_out, q_stride, (float*)rows,
+                       slots, n_rows, T, H, R, Rd, err);
+  if (dtype == SGLC_BF16)
+    return sglc_launch(latent_rope_kernel<__nv_bfloat16>, dim3(T), dim3(ROT_WARPS * 32), 0, stream, 1, true, qx,
+                       qx_stride, low, low_stride, gain, eps, positions, freq, mult, dims, pairing,
+                       (__nv_bfloat16*)q_out, q_stride, (__nv_bfloat16*)rows, slots, n_rows, T, H, R, Rd, err);
+  return SGLC_ERR_ARGUMENT;
+}

@@ -31,6 +31,7 @@ class Model:
         self.layers = [Layer(lp.name, mk("block", lp.block),
                              {role: mk(cat, spec) for role, (cat, spec) in lp.parts.items()}, lp.mixer_role())
                        for lp in plan.layers]
+        self.entries = [mk("stream_mix", spec) for spec in plan.entries]
         self.final_norm = mk("norm", plan.final_norm)
         self.head = mk("head", plan.head)
         for i, call in enumerate(plan.order):
@@ -39,9 +40,11 @@ class Model:
             if call.cache_of is not None and not (0 <= call.cache_of < i):
                 raise ValueError(f"running order entry {i} reads the cache of entry {call.cache_of}, "
                                  "which must come earlier")
+            if call.enter is not None and not (0 <= call.enter[0] < len(self.entries)):
+                raise ValueError(f"running order entry {i} names entry part {call.enter[0]}, which does not exist")
         self.weight_bytes = 0
         # a part that reads per-step host values (not only device arrays) cannot be replayed
-        parts = [self.embedding, self.position, self.final_norm, self.head]
+        parts = [self.embedding, self.position, self.final_norm, self.head] + self.entries
         for layer in self.layers:
             parts += [layer.block] + list(layer.parts.values())
         self.graph_safe = all(getattr(p, "graph_safe", True) for p in parts)
@@ -55,6 +58,7 @@ class Model:
         for layer, lp in zip(self.layers, self.plan.layers):
             pairs += [(layer.parts[role], spec) for role, (_, spec) in lp.parts.items()]
         n_layers_end = len(pairs)
+        pairs += list(zip(self.entries, self.plan.entries))
         pairs += [(self.final_norm, self.plan.final_norm), (self.head, self.plan.head)]
         for i, (part, spec) in enumerate(pairs):
             store.in_layer = n_head <= i < n_layers_end
@@ -75,7 +79,7 @@ class Model:
         E = self.plan.hidden_size
         act = 4 if self.rt.dtype == "float32" else 2
         blocks = [layer.block.workspace_per_token(layer) for layer in self.layers]
-        return 4 * E + max(blocks + [0]) + act * E
+        return 4 * E + max(blocks + [0]) + act * E + sum(p.workspace_per_token() for p in self.entries)
 
     def graph_bound(self, ctx):
         """The upper bound of the context length that this step's kernels are launched for (a
@@ -96,8 +100,12 @@ class Model:
         E = self.plan.hidden_size
         x = ctx.alloc((ctx.T, E), torch.float32)          # the residual stream, 32-bit
         self.embedding.forward(ctx, x, self.position)
+        for part in self.entries:
+            part.start(ctx, x)
         for i, call in enumerate(self.plan.order):
             layer = self.layers[call.layer]
+            if call.enter is not None:
+                self.entries[call.enter[0]].enter(ctx, x, call.enter[1])
             layer.block.forward(ctx, x, layer, cache.binding(i), self.position)
         if ctx.n_want > 0:
             hf = ctx.alloc((ctx.n_want, E), self.rt.act_dtype)

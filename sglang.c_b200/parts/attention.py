@@ -97,42 +97,75 @@ class LatentAttention(Part):
     sum_j p_j Wuv_i c_j = Wuv_i (sum_j p_j c_j), so attention runs on the latent itself as one
     shared key/value head of size kv_rank, and Wuk_iᵀ is folded into the query projection, Wuv_i
     into the output projection, once at load (in 64-bit, then rounded to the runtime's matrix
-    precision).  params: size, n_heads, qk_dim, v_dim, kv_rank, q_rank (None or a size), scale,
-    eps (of the latents' norms), own_latent, window."""
+    precision).
+
+    With `rot_dim` > 0 every query head has rot_dim more entries behind its qk_dim, and Wdkv has
+    rot_dim more rows behind the latent's: one key part that all heads share and no norm touches.
+    Both are turned by a rotary position part built from `rotary` (its params) and their dot product
+    joins the score: score = (q_i . Wuk_i c + q_i_turned . k_turned) * scale.  The cache row is then
+    [c | k_turned], the absorbed query [Wuk_i^T q_i | q_i_turned]; a head's weighted sum of rows
+    carries rot_dim entries that the folded output matrix meets with zero columns.
+    `out_mult`: a multiplier of the mixer's result, folded into the output matrix.
+    params: size, n_heads, qk_dim, v_dim, kv_rank, q_rank (None or a size), scale,
+    eps (of the latents' norms), own_latent, window, rot_dim (default 0), rotary (dims, base,
+    pairing, scaling), out_mult (default 1)."""
 
     @classmethod
     def declare_weights(cls, params):
         E, H, D, V, R = params["size"], params["n_heads"], params["qk_dim"], params["v_dim"], params["kv_rank"]
+        Rd = int(params.get("rot_dim") or 0)
         d = {"k_up": WeightDecl((H * D, R), "matrix"), "v_up": WeightDecl((H * V, R), "matrix"),
              "out_weight": WeightDecl((E, H * V), "residual_matrix")}
         if params.get("q_rank"):
             Q = params["q_rank"]
             d.update({"q_down": WeightDecl((Q, E), "matrix"), "q_norm": WeightDecl((Q,), "norm_gain"),
-                      "q_up": WeightDecl((H * D, Q), "matrix")})
+                      "q_up": WeightDecl((H * (D + Rd), Q), "matrix")})
         else:
-            d["q_weight"] = WeightDecl((H * D, E), "matrix")
+            d["q_weight"] = WeightDecl((H * (D + Rd), E), "matrix")
         if params.get("own_latent", True):
-            d.update({"kv_down": WeightDecl((R, E), "matrix"), "kv_norm": WeightDecl((R,), "norm_gain")})
+            d.update({"kv_down": WeightDecl((R + Rd, E), "matrix"), "kv_norm": WeightDecl((R,), "norm_gain")})
         return d
 
     def load(self, tensors, store):
         p = self.params
         H, D, V, R, Q = p["n_heads"], p["qk_dim"], p["v_dim"], p["kv_rank"], p.get("q_rank")
+        Rd = self.rot_dim = int(p.get("rot_dim") or 0)
+        m = float(p.get("out_mult", 1.0))
         k_up, v_up, w_o = tensors["k_up"], tensors["v_up"], tensors["out_weight"]
         q_src = tensors["q_up"] if Q else tensors["q_weight"]
 
-        def fold_queries():       # [H*R, in]: head i's rows are Wuk_iᵀ · (head i's rows of the query projection)
-            uk = k_up.tensor.double().view(H, D, R)
-            wq = q_src.tensor.double().view(H, D, -1)
-            return torch.einsum("hdr,hdi->hri", uk, wq).reshape(H * R, -1)
+        def fold_queries():       # [H*(R+Rd), in]: head i's rows are Wuk_iᵀ · (head i's plain rows of the query
+            uk = k_up.tensor.double().view(H, D, R)                      # projection), then its turned rows as they are
+            wq = q_src.tensor.double().view(H, D + Rd, -1)
+            folded = torch.einsum("hdr,hdi->hri", uk, wq[:, :D])
+            return torch.cat([folded, wq[:, D:]], 1).reshape(H * (R + Rd), -1)
 
-        def fold_output():        # [E, H*R]: head i's columns are (head i's columns of Wo) · Wuv_i
+        def fold_output():        # [E, H*(R+Rd)]: head i's columns are (head i's columns of Wo) · Wuv_i, then zeros
             uv = v_up.tensor.double().view(H, V, R)
             wo = w_o.tensor.double().view(-1, H, V)
-            return torch.einsum("ehv,hvr->ehr", wo, uv).reshape(-1, H * R)
+            folded = torch.einsum("ehv,hvr->ehr", wo, uv) * m
+            return torch.cat([folded, folded.new_zeros(folded.shape[0], H, Rd)], 2).reshape(-1, H * (R + Rd))
 
-        self.q_abs = Linear(store.computed(f"fold({k_up.name},{q_src.name})", fold_queries), None)
-        self.out = Linear(store.computed(f"fold({w_o.name},{v_up.name})", fold_output), None)
+        tag = (f",{Rd}" if Rd else "") + (f",*{m!r}" if m != 1.0 else "")
+        # with a turned part the queries leave their product in 32-bit as well (the turn is 32-bit):
+        # direct queries and the latent's projection, which read the same rows, are then one product
+        self.q_abs = self.q_and_down = None
+        if Rd and not Q and p.get("own_latent", True):
+            kv = tensors["kv_down"]
+            self.q_and_down = Linear(store.computed(
+                f"fold({k_up.name},{q_src.name}{tag})+{kv.name}",
+                lambda: torch.cat([fold_queries(), kv.tensor.double()], 0)), None)
+        else:
+            self.q_abs = Linear(store.computed(f"fold({k_up.name},{q_src.name}{tag})", fold_queries), None)
+        self.out = Linear(store.computed(f"fold({w_o.name},{v_up.name}{tag})", fold_output), None)
+        self.rotary = None
+        if Rd:
+            from .registry import get_part
+            rot = dict(p.get("rotary") or {"dims": 0, "base": 10000.0})
+            if int(rot.get("dims", 0)) > Rd:
+                raise ValueError(f"latent attention: {rot['dims']} turned entries do not fit a turned part of {Rd}")
+            self.rotary = get_part("position", "rotary")(rot, self.rt)
+            self.rotary.load({}, store)
         self.q_norm = self.kv_norm = None
         downs = []
         if Q:
@@ -143,18 +176,20 @@ class LatentAttention(Part):
             self.kv_norm = store.vector(tensors["kv_norm"])
         # the projections whose results go through a norm are one product with a 32-bit result
         self.down = None
-        if downs:
+        if downs and self.q_and_down is None:
             self.down = Linear(store.computed("+".join(r.name for r in downs),
                                               lambda: torch.cat([r.tensor.float() for r in downs], 0)), None)
 
     def cache_need(self):
         p = self.params
-        return CacheNeed.paged_kv(1, p["kv_rank"], p.get("window"), shared=True)
+        return CacheNeed.paged_kv(1, p["kv_rank"] + int(p.get("rot_dim") or 0), p.get("window"), shared=True)
 
     def workspace_per_token(self):
         p = self.params
         act = 4 if self.rt.dtype == "float32" else 2
-        return act * (2 * p["n_heads"] * p["kv_rank"] + (p.get("q_rank") or 0)) + 4 * ((p.get("q_rank") or 0) + p["kv_rank"])
+        W, Q = p["kv_rank"] + int(p.get("rot_dim") or 0), p.get("q_rank") or 0
+        turned = 4 * (p["n_heads"] + 1) * W + 1024 if p.get("rot_dim") else 0
+        return act * (2 * p["n_heads"] * W + Q) + 4 * (Q + W) + turned
 
     def forward(self, ctx, h, residual, cache, position=None, out=None):
         from ..csrc import ops
@@ -166,6 +201,8 @@ class LatentAttention(Part):
         T = h.shape[0]
         eps = float(p["eps"])
         grp = ctx.group(cache.group)
+        if self.rot_dim:
+            return self._forward_turned(ctx, h, residual, cache, grp, out)
         q_in = h
         if self.down is not None:
             low = ctx.alloc((T, self.down.out_size), torch.float32)
@@ -181,6 +218,108 @@ class LatentAttention(Part):
         self.q_abs.forward(ctx, q_in, out=q)
         o = ctx.alloc((T, H * R), self.rt.act_dtype)
         ctx.rt.attend_shared(ctx, q, cache, grp, o, H, R, float(p["scale"]), p.get("window"))
+        return self.out.forward(ctx, o, out=out, residual=residual)
+
+    def _forward_turned(self, ctx, h, residual, cache, grp, out):
+        """The form with a turned part: queries and the latent's row leave their products in 32-bit;
+        one launch norms the latent, turns the shared key part and every head's turned entries, and
+        writes the row into the cache and the queries in the activation precision."""
+        from ..csrc import ops
+        p = self.params
+        H, R, Rd, Q = p["n_heads"], p["kv_rank"], self.rot_dim, p.get("q_rank") or 0
+        own = p.get("own_latent", True)
+        T, W = h.shape[0], R + Rd
+        eps = float(p["eps"])
+        low = None
+        if self.q_and_down is not None:
+            pre = ctx.alloc((T, H * W + W), torch.float32)
+            self.q_and_down.forward(ctx, h, out=pre)
+            qx, low = ctx.columns(pre, 0, H * W), ctx.columns(pre, H * W, H * W + W)
+        else:
+            q_in = h
+            if self.down is not None:
+                lows = ctx.alloc((T, self.down.out_size), torch.float32)
+                self.down.forward(ctx, h, out=lows)
+                if Q:
+                    q_in = ctx.alloc((T, Q), self.rt.act_dtype)
+                    ops.norm_rows(ctx.columns(lows, 0, Q), self.q_norm, None, eps, q_in, form="rms")
+                if own:
+                    low = ctx.columns(lows, Q, Q + W)
+            qx = ctx.alloc((T, H * W), torch.float32)
+            self.q_abs.forward(ctx, q_in, out=qx)
+        q = ctx.alloc((T, H * W), self.rt.act_dtype)
+        rot = self.rotary
+        ops.latent_rope(qx, low, self.kv_norm, eps, ctx.positions, rot.frequencies, rot.multiplier, rot.dims,
+                        rot.pairing, q, cache.tensor.view(-1, W) if own else None, grp.slots, H, R, Rd)
+        o = ctx.alloc((T, H * W), self.rt.act_dtype)
+        ctx.rt.attend_shared(ctx, q, cache, grp, o, H, W, float(p["scale"]), p.get("window"))
+        return self.out.forward(ctx, o, out=out, residual=residual)
+
+
+@register_part("mixer", "talking_attention")
+class TalkingHeadsAttention(Part):
+    """Softmax attention whose heads exchange their weights after the softmax, with grouped key
+    heads that are also the values:
+        q = h Wq^T, k = h Wk^T (n_kv_heads x head_dim), v = k as projected;
+        q^, k^: each head divided by its root mean square (eps) times a gain of head_dim entries
+        (one for the queries, one for the keys; the heads share them);
+        s_a(i, j) = (q^_a(i) . k^_c(j)) * scale - slope_a (i - j),  c = a / (n_heads / n_kv_heads),
+        slope_a = 2^(-slope_span (a + 1) / n_heads), over 0 <= i - j < window (all j <= i without);
+        p_a = softmax_j s_a;   p'_a = sum_b talk[a][b] p_b;   o_a(i) = sum_j p'_a(i, j) v_c(j);
+        result = Wo (o * sigmoid(h Wg^T)) * out_mult.
+    The three input projections are one product with a 32-bit result; the cache keeps one row per
+    position and key head, the key as projected (its 1/rms is formed where it is read).  Norms,
+    scores, weights, their mix and the gate are 32-bit.
+    params: size, n_heads, n_kv_heads, head_dim, scale, window, eps, slope_span (default 8),
+    out_mult (default 1)."""
+
+    @classmethod
+    def declare_weights(cls, params):
+        E, H, G, D = (params[k] for k in ("size", "n_heads", "n_kv_heads", "head_dim"))
+        return {"q_weight": WeightDecl((H * D, E), "matrix"), "k_weight": WeightDecl((G * D, E), "matrix"),
+                "q_norm": WeightDecl((D,), "norm_gain"), "k_norm": WeightDecl((D,), "norm_gain"),
+                "talk": WeightDecl((H, H), "mixing"), "gate_weight": WeightDecl((H * D, E), "matrix"),
+                "out_weight": WeightDecl((E, H * D), "residual_matrix")}
+
+    def load(self, tensors, store):
+        p = self.params
+        H = p["n_heads"]
+        refs = [tensors[k] for k in ("q_weight", "k_weight", "gate_weight")]
+        pad = (-sum(r.tensor.shape[0] for r in refs)) % 8
+        self.inp = Linear(store.computed("+".join(r.name for r in refs) + f"+{pad}", lambda: torch.cat(
+            [r.tensor.float() for r in refs] + [torch.zeros(pad, refs[0].tensor.shape[1])], 0)), None)
+        self.q_norm, self.k_norm = store.vector(tensors["q_norm"]), store.vector(tensors["k_norm"])
+        self.talk = store.vector(tensors["talk"])
+        self.out = Linear(store.matrix(tensors["out_weight"]), None)
+        span = float(p.get("slope_span", 8.0))
+        slopes = torch.tensor([2.0 ** (-span * (a + 1) / H) for a in range(H)], dtype=torch.float64)
+        self.slopes = slopes.to(torch.float32).to(self.rt.device)
+
+    def cache_need(self):
+        p = self.params
+        return CacheNeed.paged_kv(p["n_kv_heads"], p["head_dim"], p.get("window"), shared=True)
+
+    def workspace_per_token(self):
+        p = self.params
+        H, G, D = p["n_heads"], p["n_kv_heads"], p["head_dim"]
+        act = 4 if self.rt.dtype == "float32" else 2
+        return 4 * ((2 * H + G) * D + 8) + 4 * H * D + act * H * D + 1024
+
+    def forward(self, ctx, h, residual, cache, position=None, out=None):
+        from ..csrc import ops
+        p = self.params
+        H, G, D = p["n_heads"], p["n_kv_heads"], p["head_dim"]
+        T = h.shape[0]
+        eps = float(p["eps"])
+        grp = ctx.group(cache.group)
+        pre = ctx.alloc((T, self.inp.out_size), torch.float32)
+        self.inp.forward(ctx, h, out=pre)
+        q = ctx.alloc((T, H * D), torch.float32)
+        ops.talk_prep(pre, self.q_norm, self.k_norm, eps, q, cache.tensor, grp.slots, H, G, D, grp.page_size)
+        o = ctx.alloc((T, H * D), self.rt.act_dtype)
+        ops.talk_attention(q, cache.tensor, grp.block_table, ctx.token_req, ctx.positions, self.slopes, self.talk,
+                           ctx.columns(pre, (H + G) * D, (2 * H + G) * D), o, H, G, D, grp.page_size,
+                           float(p["scale"]), eps, float(p.get("out_mult", 1.0)), p.get("window"))
         return self.out.forward(ctx, o, out=out, residual=residual)
 
 
@@ -219,6 +358,8 @@ class RotaryAttention(Part):
         rot = self.params.get("rotary") or {"dims": 0, "base": 10000.0, "scaling": None}
         self.rotary = get_part("position", "rotary")(rot, self.rt)
         self.rotary.load({}, store)
+        if self.rotary.pairing != "halves":
+            raise ValueError("rotary_attention: its kernel turns pairs (i, i + dims/2) only")
 
     def cache_need(self):
         p = self.params

@@ -71,9 +71,20 @@ class MLP(Part):
 
 @register_part("feed_forward", "gated_mlp")
 class GatedMLP(Part):
-    """residual += (silu(h Wg^T + bg) * (h Wu^T + bu)) Wd^T + bd.  Gate and up projections are one
-    product; the gating runs on its result; the down projection adds into the stream.
-    params: size, inner_size, bias."""
+    """residual += m (act(h Wg^T + bg) * (h Wu^T + bu)) Wd^T + bd.  Gate and up projections are one
+    product; the gating runs on its result; the down projection adds into the stream.  The
+    multiplier m of the sublayer's result is taken by the gating kernel, in 32-bit, ahead of the
+    down projection (which is linear), so a model with m != 1 and a down bias is not served.
+    params: size, inner_size, bias, activation ("silu", the default, or "gelu_tanh"), out_mult (m,
+    default 1)."""
+
+    def __init__(self, params, runtime):
+        super().__init__(params, runtime)
+        from ..csrc import ops
+        if self.params.get("activation", "silu") not in ops.GATE_ACTS:
+            raise ValueError(f"gated_mlp: activation {self.params['activation']!r}; known: {sorted(ops.GATE_ACTS)}")
+        if float(self.params.get("out_mult", 1.0)) != 1.0 and self.params.get("bias", True):
+            raise ValueError("gated_mlp: a result multiplier does not go with a bias on the down projection")
 
     @classmethod
     def declare_weights(cls, params):
@@ -106,7 +117,7 @@ class GatedMLP(Part):
         gu = ctx.alloc((T, 2 * F), self.rt.act_dtype)
         self.gate_up.forward(ctx, h, out=gu)
         z = ctx.alloc((T, F), self.rt.act_dtype)
-        ops.gated_act(gu, z)
+        ops.gated_act(gu, z, act=self.params.get("activation", "silu"), mult=float(self.params.get("out_mult", 1.0)))
         return self.down.forward(ctx, z, out=out, residual=residual)
 
 

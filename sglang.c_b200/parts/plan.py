@@ -17,7 +17,8 @@ class WeightDecl:
     names the tensor's role for random initialisation: "matrix",
     "residual_matrix" (a projection back into the residual stream),
     "embedding", "bias", "norm_gain", "norm_bias", "conv_taps" (the taps of a short convolution
-    over time, [channels, taps]).  `kind` is "float" or "int"
+    over time, [channels, taps]), "fraction" (numbers in [0, 1)), "mixing" (a square matrix near
+    the identity), "carry" ([n, 2n], near [identity | 0]).  `kind` is "float" or "int"
     (integer tables stay int32)."""
     shape: Tuple[int, ...]
     init: str
@@ -81,9 +82,12 @@ class LayerPlan:
 class LayerCall:
     """One entry of the running order.  `layer` indexes `ModelPlan.layers`.
     `cache_of` is None when this call keeps a cache of its own, else the index
-    (in `order`) of the earlier call whose cache it reads without writing."""
+    (in `order`) of the earlier call whose cache it reads without writing.
+    `enter` = (index into `ModelPlan.entries`, pass number): that part's `enter(ctx, x, pass)`
+    runs right before this call (the first layer of a pass of a repeated group)."""
     layer: int
     cache_of: Optional[int] = None
+    enter: Optional[Tuple[int, int]] = None
 
 
 @dataclass
@@ -102,6 +106,9 @@ class ModelPlan:
     ignorable: Tuple[str, ...] = ()
     # prefixes to try when a name is not found as written
     name_prefixes: Tuple[str, ...] = ("",)
+    # parts of category stream_mix that act between layers: each sees the embedding output
+    # (`start(ctx, x)`) and runs where a LayerCall's `enter` names it
+    entries: List[PartSpec] = field(default_factory=list)
 
     def part_specs(self):
         yield self.embedding
@@ -109,5 +116,7 @@ class ModelPlan:
         for layer in self.layers:
             for _, spec in layer.parts.values():
                 yield spec
+        for spec in self.entries:
+            yield spec
         yield self.final_norm
         yield self.head

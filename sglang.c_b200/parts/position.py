@@ -69,7 +69,9 @@ class RotaryPositions(PositionEncoding):
     f_i / factor * ramp_i + f_i (1 - ramp_i), and cos and sin are both multiplied by
     0.1 ln(factor) + 1.  The table is made once, in 64-bit; the mixer's kernel forms the angles.
     A mixer builds this part from its own params (a model may turn each layer differently).
-    params: dims, base, scaling (None or the four numbers)."""
+    `pairing` "neighbours" pairs entry 2i with 2i+1 instead (for the kernels that take the choice).
+    params: dims, base, scaling (None or the four numbers), pairing ("halves", the default, or
+    "neighbours")."""
 
     def load(self, tensors, store):
         import math
@@ -89,3 +91,6 @@ class RotaryPositions(PositionEncoding):
             self.multiplier = 0.1 * math.log(factor) + 1.0
         self.frequencies = f.contiguous().to(self.rt.device) if self.rt is not None else f
         self.dims = dims
+        self.pairing = self.params.get("pairing", "halves")
+        if self.pairing not in ("halves", "neighbours"):
+            raise ValueError(f"rotary: pairing {self.pairing!r}; known: halves, neighbours")

@@ -192,3 +192,67 @@ class LinearDecayAttention(Part):
         ops.gated_norm(o, ctx.columns(pre, 2 * H * D + H * V, 2 * H * D + 2 * H * V), self.norm, z, 1, H * V,
                        float(p["eps"]), "sigmoid")
         return self.out.forward(ctx, z, out=out, residual=residual)
+
+
+@register_part("mixer", "hgrn2")
+class RowGatedState(Part):
+    """HGRN2: linear attention whose forget gate also says how much is written.  Per head a matrix
+    state S [dim x v_dim]; with q = silu(h Wq^T), v = h Wv^T and, per head and row, the gate
+    f = l + (1 - l) sigmoid(h Wf^T + bf), l a learned lower bound,
+        S <- diag(f) S + (1 - f) v^T;   o = S^T q
+    (no key and no other scale).  Each head's o is divided by its root mean square (eps) and
+    multiplied by a gain of v_dim entries that the heads share; the heads side by side go through
+    the output projection.  The three input projections are one product with a 32-bit result;
+    gates, state and the norm are 32-bit.  S starts at zero and is carried per request.
+    params: size, n_heads, dim, v_dim, eps, out_mult (a multiplier of the mixer's result, default
+    1, folded into the norm's gain)."""
+
+    @classmethod
+    def declare_weights(cls, params):
+        E, H, D, V = (params[k] for k in ("size", "n_heads", "dim", "v_dim"))
+        return {"q_weight": WeightDecl((H * D, E), "matrix"), "gate_weight": WeightDecl((H * D, E), "matrix"),
+                "gate_bias": WeightDecl((H * D,), "bias"), "lower": WeightDecl((H * D,), "fraction"),
+                "v_weight": WeightDecl((H * V, E), "matrix"), "norm": WeightDecl((V,), "norm_gain"),
+                "out_weight": WeightDecl((E, H * V), "residual_matrix")}
+
+    def load(self, tensors, store):
+        p = self.params
+        H, D, V = p["n_heads"], p["dim"], p["v_dim"]
+        refs = [tensors[k] for k in ("q_weight", "gate_weight", "v_weight")]
+        pad = (-(2 * H * D + H * V)) % 8
+        self.inp_w = store.computed("+".join(r.name for r in refs) + f"+{pad}", lambda: torch.cat(
+            [r.tensor.float() for r in refs] + [torch.zeros(pad, refs[0].tensor.shape[1])], 0))
+        fb = tensors["gate_bias"]
+        bias = store.computed(f"0+{fb.name}+0+{pad}", kind="vector", make=lambda: torch.cat(
+            [torch.zeros(H * D), fb.tensor.float(), torch.zeros(H * V + pad)]))
+        self.inp = Linear(self.inp_w, bias)
+        self.lower = store.vector(tensors["lower"])
+        m = float(p.get("out_mult", 1.0))
+        g = tensors["norm"]
+        self.norm = store.vector(g) if m == 1.0 else store.computed(
+            f"{g.name}*{m!r}", kind="vector", make=lambda: (g.tensor.double() * m).float())
+        self.out = Linear(store.matrix(tensors["out_weight"]), None)
+
+    def cache_need(self):
+        p = self.params
+        return CacheNeed.state((p["n_heads"], p["dim"], p["v_dim"]), "float32")
+
+    def workspace_per_token(self):
+        p = self.params
+        H, D, V = p["n_heads"], p["dim"], p["v_dim"]
+        act = 4 if self.rt.dtype == "float32" else 2
+        return 4 * (2 * H * D + H * V + 8) + 4 * H * V + act * H * V + 1024
+
+    def forward(self, ctx, h, residual, cache, position=None, out=None):
+        p = self.params
+        H, D, V = p["n_heads"], p["dim"], p["v_dim"]
+        T = h.shape[0]
+        pre = ctx.alloc((T, self.inp.out_size), torch.float32)
+        self.inp.forward(ctx, h, out=pre)
+        o = ctx.alloc((T, H * V), torch.float32)
+        ops.matrix_state("row_gate", ctx.columns(pre, 0, H * D), ctx.columns(pre, H * D, 2 * H * D),
+                         ctx.columns(pre, 2 * H * D, 2 * H * D + H * V), o, cache.tensor, ctx.q_start,
+                         ctx.state_slots, ctx.R, H, H, D, V, silu_in=True, lower=self.lower)
+        z = ctx.alloc((T, H * V), self.rt.act_dtype)
+        ops.gated_norm(o, None, self.norm, z, H, V, float(p["eps"]), "none")
+        return self.out.forward(ctx, z, out=out, residual=residual)

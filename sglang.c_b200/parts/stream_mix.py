@@ -39,3 +39,40 @@ class DepthWeightedAverage(Part):
     def finish(self, ctx, x):
         ops.depth_mix(x, ctx.shared["depth_streams"], self.params["index"] + 2, self.weights)
         return x
+
+
+@register_part("stream_mix", "input_reentry")
+class InputReentry(Part):
+    """Ahead of pass t of a group of layers that runs several times over with the same weights, the
+    stream is remade from itself and the embedding output X_0 of the same tokens:
+        x <- W [x ; X_0] + step[t]        (W [size, 2 size], x's columns first; step [times, size]).
+    `start` (after the embedding) takes a buffer of 2 size columns in the activation precision
+    from the step workspace, below the layers' buffers, and puts X_0 into its right half once;
+    `enter` puts x into the left half and runs the product, whose 32-bit result replaces x, with
+    step[t] as its bias.  params: size, times."""
+
+    @classmethod
+    def declare_weights(cls, params):
+        E = params["size"]
+        return {"in_weight": WeightDecl((E, 2 * E), "carry"), "steps": WeightDecl((params["times"], E), "bias")}
+
+    def load(self, tensors, store):
+        from .linear import Linear
+        self.inp = Linear(store.matrix(tensors["in_weight"]), None)
+        steps = store.vector(tensors["steps"])
+        self.steps = [steps[t] for t in range(self.params["times"])]
+
+    def workspace_per_token(self):
+        return (4 if self.rt.dtype == "float32" else 2) * 2 * self.params["size"] + 256
+
+    def start(self, ctx, x):
+        E = self.params["size"]
+        rows = ctx.alloc((x.shape[0], 2 * E), self.rt.act_dtype)
+        ctx.shared[("input_reentry", id(self))] = rows
+        ops.cast_rows(x, ctx.columns(rows, E, 2 * E))
+
+    def enter(self, ctx, x, t):
+        rows = ctx.shared[("input_reentry", id(self))]
+        ops.cast_rows(x, ctx.columns(rows, 0, self.params["size"]))
+        ctx.rt.gemm(rows, self.inp.weight, self.steps[t], out=x, few_ok=ctx.few_token_ok)
+        return x

@@ -61,6 +61,8 @@ def _category_of(plan, spec):
         for cat, s in layer.parts.values():
             if spec is s:
                 return cat
+    if any(spec is s for s in plan.entries):
+        return "stream_mix"
     raise WeightError("part spec does not belong to the plan")
 
 

@@ -51,6 +51,12 @@ def random_tensor(seed, name, decl, scheme, n_layers, vocab_size=None):
         a = rng.standard_normal(shape) * std if scheme == "varied" else np.zeros(shape)
     elif decl.init == "conv_taps":
         a = rng.standard_normal(shape) * 0.4
+    elif decl.init == "fraction":              # a bound or a share in [0, 1)
+        a = rng.random(shape) * 0.9
+    elif decl.init == "mixing":                # a square matrix that mixes heads: near one on the diagonal
+        a = np.eye(shape[0], shape[1]) * (1.0 if scheme == "standard" else 0.8) + rng.standard_normal(shape) * 0.2
+    elif decl.init == "carry":                 # [n, 2n]: passes its first n inputs on, plus a little of everything
+        a = np.eye(shape[0], shape[1]) + rng.standard_normal(shape) * std
     elif decl.init == "norm_gain":
         a = 1.0 + rng.standard_normal(shape) * 0.1 if scheme == "varied" else np.ones(shape)
     elif decl.init == "norm_bias":
