@@ -18,8 +18,8 @@ requests) over its time, against the measured copy bandwidth; `points` has decod
 at batch 1 and 64, the true 32-bit path and the prefill through the C interface;
 `kernels` says where a decode and a
 prefill step's time goes, kernel by kernel.  `--full` adds medium and XL layer
-sizes and the mixed workload to `points`.  `--compare tukavik` (or `zuretar`, which adds that design as a third column) measures, instead of all
-this, a Tukavik model beside the GPT-2 model of the same layer sizes.
+sizes and the mixed workload to `points`.  `--compare tukavik` (or `zuretar`, or `buborax`, each of which adds its design as one more column) measures,
+instead of all this, a Tukavik model beside the GPT-2 model of the same layer sizes.
 """
 import argparse
 import atexit
@@ -768,11 +768,70 @@ def zuretar_step_bytes(cfg, batch, context, prompt_tokens):
     return out
 
 
+def buborax_config(base, n_layer):
+    """A Buborax model with the layer sizes of a GPT-2 model: the same width, head count, head size
+    (64), vocabulary and number of layer runs.  Layers in threes: an HGRN2 recurrence (the model's heads,
+    keys and values of 64); latent attention (the model's heads of 64 plus 64 turned entries over a
+    latent of 64, so a cached row of 128; window 256); talking-heads attention (the model's heads over a
+    quarter as many key heads, window 256).  Every layer has a gated feed-forward of two thirds the
+    width of GPT-2's.  Layers 3..5 run twice, so the file holds three layers fewer than run."""
+    E, H, I = base["n_embd"], base["n_head"], base["n_inner"]
+    mlp = {"kind": "dense", "ff": max(64, (2 * I // 3) // 64 * 64)}
+    kinds = [{"type": "hgrn2", "mixer": {"heads": H, "dim": 64, "vdim": 64}, "mlp": mlp},
+             {"type": "latent_attention",
+              "mixer": {"heads": H, "dim": 64, "rot_dim": 64, "vdim": 64, "kv_rank": 64, "scale": 128 ** -0.5,
+                        "mask": {"size": 256}, "rot": {"base": 10000.0, "dims": 64}}, "mlp": mlp},
+             {"type": "attention", "mixer": {"heads": H, "kv_heads": max(1, H // 4), "dim": 64, "vdim": 64, "scale": 0.125,
+                                             "mask": {"size": 256}}, "mlp": mlp}]
+    n = max(6, n_layer - 3)
+    return {"architecture": "Buborax", "vocab": base["vocab_size"], "width": E, "residual_mult": 0.5,
+            "norm": {"eps": 1e-5, "groups": 4}, "loop": {"start": 3, "stop": 6, "times": 2},
+            "layers": [kinds[i % 3] for i in range(n)], "max_positions": base["n_positions"]}
+
+
+def buborax_step_bytes(cfg, batch, context, prompt_tokens):
+    """What the kernels that this design adds or extends must move in a step (32-bit projections,
+    states and read-outs; bfloat16 activations and cache): {decode | prefill: {kernel label: bytes}}.
+    The talking-heads attention is counted as every query reading the keys of its window once (the
+    rows are the values too)."""
+    lp = cfg["loop"]
+    runs = list(range(lp["start"])) + list(range(lp["start"], lp["stop"])) * lp["times"] + \
+        list(range(lp["stop"], len(cfg["layers"])))
+    E = cfg["width"]
+    out = {}
+    for name, T, R in (("decode", batch, batch), ("prefill", prompt_tokens, 2)):
+        state = gnorm = rope = prep = talk = gact = norm = cast = 0
+        for i in runs:
+            layer = cfg["layers"][i]
+            m = layer["mixer"]
+            norm += 2 * T * E * (4 + 2)
+            if layer["type"] == "hgrn2":
+                hd, hv = m["heads"] * m["dim"], m["heads"] * m["vdim"]
+                state += R * m["heads"] * m["dim"] * m["vdim"] * 8 + T * (2 * hd + 2 * hv) * 4
+                gnorm += T * hv * (4 + 2)
+            elif layer["type"] == "latent_attention":
+                W = m["kv_rank"] + m["rot_dim"]
+                rope += T * (m["heads"] + 1) * W * (4 + 2)
+            else:
+                H, G, D = m["heads"], m["kv_heads"], m["dim"]
+                prep += T * (H + G) * D * 4 + T * H * D * 4 + T * G * D * 2
+                seen = min(context, m["mask"]["size"])
+                talk += T * seen * G * D * 2 + T * H * D * (4 + 4 + 2)
+            gact += T * layer["mlp"]["ff"] * 6
+        cast = lp["times"] * T * E * (4 + 2) + T * E * (4 + 2)
+        out[name] = {"matrix_state": state, "gated_norm": gnorm, "latent_rope": rope, "talk_prep": prep,
+                     "talk_attention": talk, "gated_act": gact, "norm_rows": norm, "cast_rows": cast}
+    return out
+
+
 DESIGNS = {"tukavik": (tukavik_config, tukavik_step_bytes,
                        {"mingru_scan": "mingru_scan", "norm_rows": "norm_rows", "depth_mix": "depth_mix",
                         "attention_decode_shared": "attention_shared"}),
            "zuretar": (zuretar_config, zuretar_step_bytes,
-                       {k: k for k in ("short_conv", "matrix_state", "gated_norm", "rotary_kv", "attention_ext", "gated_act")})}
+                       {k: k for k in ("short_conv", "matrix_state", "gated_norm", "rotary_kv", "attention_ext", "gated_act")}),
+           "buborax": (buborax_config, buborax_step_bytes,
+                       {k: k for k in ("matrix_state", "gated_norm", "latent_rope", "talk_prep", "talk_attention",
+                                       "gated_act", "norm_rows", "cast_rows")})}
 
 
 def compare_designs(designs, sizes, steps, warmup, pk):
@@ -898,7 +957,7 @@ def main():
     ap.add_argument("--only", default=None, choices=["decode", "prefill", "fp32"],
                     help="a handful of steps of one kind and nothing else (what a profiler is pointed at): "
                          "decode steps at batch 8, prefill steps of 2 x 1,024 tokens, or both on the 32-bit path")
-    ap.add_argument("--compare", default=None, choices=["tukavik", "zuretar"],
+    ap.add_argument("--compare", default=None, choices=["tukavik", "zuretar", "buborax"],
                     help="nothing of the above: decode and prefill of a model of this design beside the GPT-2 model "
                          "of equal layer sizes (--model, or small and medium with --full), with both kernel tables")
     args = ap.parse_args()
@@ -918,7 +977,8 @@ def main():
     if args.compare:
         clocks = ClockSampler()
         clocks.start()
-        designs = ["tukavik", "zuretar"] if args.compare == "zuretar" else ["tukavik"]
+        designs = {"tukavik": ["tukavik"], "zuretar": ["tukavik", "zuretar"],
+                   "buborax": ["tukavik", "zuretar", "buborax"]}[args.compare]
         res = compare_designs(designs, ["small", "medium"] if args.full else [args.model], steps, warmup, pk)
         print(json.dumps({"metric": f"decode and prefill tok/s, {' and '.join(d.capitalize() for d in designs)} beside "
                                     "GPT-2 at equal layer sizes (Python engine)",

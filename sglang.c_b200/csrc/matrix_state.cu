@@ -118,9 +118,11 @@ matrix_state_kernel(MsArgs p) {
       if (x < MS_BATCH * DP) {
         const int b = x / DP, i = x % DP, at = b * SP + i / MS_PER * LP + i % MS_PER;
         if (MODE == MS_ROWGATE) {
-          // (rows beyond the key size keep a gate of one: their entries stay zero)
+          // What is staged is 1 - f = (1 - l) sigmoid(-x), the share of the value a row takes in:
+          // formed from f itself it would lose its digits where f is close to one.
+          // (rows beyond the key size take in nothing: their entries stay zero)
           const float lo = i < p.D ? __ldg(p.lower + (size_t)g * p.D + i) : 1.0f;
-          ks[buf][at] = lo + (1.0f - lo) * (1.0f / (1.0f + expf(-rk[n])));
+          ks[buf][at] = (1.0f - lo) * (1.0f / (1.0f + expf(rk[n])));
         } else {
           ks[buf][at] = p.silu_in ? ms_silu(rk[n]) : rk[n];
         }
@@ -188,10 +190,10 @@ matrix_state_kernel(MsArgs p) {
       } else if (MODE == MS_ROWGATE) {
 #pragma unroll
         for (int e = 0; e < MS_PER; e += 4) {
-          S[e] = fmaf(kk[e], S[e], (1.0f - kk[e]) * vv);
-          S[e + 1] = fmaf(kk[e + 1], S[e + 1], (1.0f - kk[e + 1]) * vv);
-          S[e + 2] = fmaf(kk[e + 2], S[e + 2], (1.0f - kk[e + 2]) * vv);
-          S[e + 3] = fmaf(kk[e + 3], S[e + 3], (1.0f - kk[e + 3]) * vv);
+          S[e] = fmaf(kk[e], vv - S[e], S[e]);
+          S[e + 1] = fmaf(kk[e + 1], vv - S[e + 1], S[e + 1]);
+          S[e + 2] = fmaf(kk[e + 2], vv - S[e + 2], S[e + 2]);
+          S[e + 3] = fmaf(kk[e + 3], vv - S[e + 3], S[e + 3]);
           o0 = fmaf(S[e], qq[e], o0);
           o1 = fmaf(S[e + 1], qq[e + 1], o1);
           o2 = fmaf(S[e + 2], qq[e + 2], o2);

@@ -9,12 +9,16 @@ from .registry import register_part
 class PreNormBlock(Part):
     """x += mixer(norm1(x)); x += ffn(norm2(x))  (reference src/gpt2.c:219-293).
     The residual stream x stays 32-bit; the normalised rows are in the
-    runtime's activation precision."""
+    runtime's activation precision.  The second sublayer is there only if the layer has an
+    `ffn`.  (A model that multiplies every sublayer's result by a constant gives that constant
+    to the sublayers' parts, which take it ahead of their last product.)"""
 
     def workspace_per_token(self, layer):
         act = 4 if self.rt.dtype == "float32" else 2
-        return act * layer.norm1.params["size"] + max(layer.mixer.workspace_per_token(),
-                                                      layer.ffn.workspace_per_token())
+        inner = layer.mixer.workspace_per_token()
+        if "ffn" in layer.parts:
+            inner = max(inner, layer.ffn.workspace_per_token())
+        return act * layer.norm1.params["size"] + inner
 
     def forward(self, ctx, x, layer, cache, position=None):
         T = x.shape[0]
@@ -24,8 +28,9 @@ class PreNormBlock(Part):
         inner = ctx.mark()
         layer.mixer.forward(ctx, h, residual=x, cache=cache, position=position)
         ctx.release(inner)               # the mixer's buffers make room for the feed-forward's
-        layer.norm2.forward(ctx, x, h)
-        layer.ffn.forward(ctx, h, residual=x)
+        if "ffn" in layer.parts:
+            layer.norm2.forward(ctx, x, h)
+            layer.ffn.forward(ctx, h, residual=x)
         ctx.release(mark)
         return x
 

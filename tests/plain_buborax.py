@@ -100,6 +100,31 @@ def head_slopes(heads):
     return np.array([2.0 ** (-8.0 * (h + 1) / heads) for h in range(heads)])
 
 
+def mask_size(m):
+    return (m.get("mask") or {}).get("size")
+
+
+def talking_heads(q, k, gain_q, gain_k, talk, scale, size, eps):
+    """q [n, H, D], k [n, G, D] as projected -> [n, H, D]: per-head RMS norm of both, scores with a
+    linear distance penalty per head, window, softmax, the heads' weights mixed by `talk`, applied
+    to the keys as projected."""
+    n, H, D = q.shape
+    G = k.shape[1]
+    qn, kn = rms_norm(q, gain_q, eps), rms_norm(k, gain_k, eps)
+    vis = window_mask(n, size)
+    dist = (np.arange(n)[:, None] - np.arange(n)[None, :]).astype(np.float64)
+    slopes = head_slopes(H)
+    P = np.zeros((H, n, n))
+    for a in range(H):
+        s = qn[:, a] @ kn[:, a // (H // G)].T * scale - slopes[a] * dist
+        P[a] = softmax_rows(s, vis)
+    Pm = np.einsum("hg,gij->hij", talk, P)
+    o = np.zeros((n, H, D))
+    for a in range(H):
+        o[:, a] = Pm[a] @ k[:, a // (H // G)]
+    return o
+
+
 def talking_attention(h, w, p, m, eps):
     """Softmax attention whose values are the un-normed keys, with a linear distance penalty per
     head, a sliding window, the heads' weights mixed after the softmax, and a sigmoid output gate."""
@@ -107,22 +132,22 @@ def talking_attention(h, w, p, m, eps):
     H, G, D = m["heads"], m["kv_heads"], m["dim"]
     q = (h @ w[p + "q"].T).reshape(n, H, D)
     k = (h @ w[p + "k"].T).reshape(n, G, D)
-    v = k
-    qn = rms_norm(q, w[p + "q.norm"], eps)
-    kn = rms_norm(k, w[p + "k.norm"], eps)
-    vis = window_mask(n, m["mask"]["size"])
-    dist = (np.arange(n)[:, None] - np.arange(n)[None, :]).astype(np.float64)
-    slopes = head_slopes(H)
-    P = np.zeros((H, n, n))
-    for a in range(H):
-        s = qn[:, a] @ kn[:, a // (H // G)].T * m["scale"] - slopes[a] * dist
-        P[a] = softmax_rows(s, vis)
-    Pm = np.einsum("hg,gij->hij", w[p + "talk"], P)
-    o = np.zeros((n, H, D))
-    for a in range(H):
-        o[:, a] = Pm[a] @ v[:, a // (H // G)]
+    o = talking_heads(q, k, w[p + "q.norm"], w[p + "k.norm"], w[p + "talk"], m["scale"], mask_size(m), eps)
     o = o.reshape(n, H * D) * sigmoid(h @ w[p + "g"].T)
     return o @ w[p + "o"].T
+
+
+def row_gated_state(q, f, v, S=None):
+    """q, f [n, H, D], v [n, H, V]: S <- diag(f_t) S + (1 - f_t) v_t^T, o_t = S^T q_t, token by
+    token from S (zero if not given).  Returns (o [n, H, V], the last S [H, D, V])."""
+    n, H, D = q.shape
+    V = v.shape[2]
+    S = np.zeros((H, D, V)) if S is None else S.copy()
+    o = np.zeros((n, H, V))
+    for t in range(n):
+        S = f[t][:, :, None] * S + (1.0 - f[t])[:, :, None] * v[t][:, None, :]
+        o[t] = np.einsum("hdv,hd->hv", S, q[t])
+    return o, S
 
 
 def hgrn2(h, w, p, m, eps):
@@ -134,11 +159,7 @@ def hgrn2(h, w, p, m, eps):
     v = (h @ w[p + "v"].T).reshape(n, H, V)
     low = w[p + "lower"]
     f = (low + (1.0 - low) * sigmoid(h @ w[p + "f"].T + w[p + "f.b"])).reshape(n, H, D)
-    S = np.zeros((H, D, V))
-    o = np.zeros((n, H, V))
-    for t in range(n):
-        S = f[t][:, :, None] * S + (1.0 - f[t])[:, :, None] * v[t][:, None, :]
-        o[t] = np.einsum("hdv,hd->hv", S, q[t])
+    o, _ = row_gated_state(q, f, v)
     o = rms_norm(o, w[p + "norm"], eps).reshape(n, H * V)
     return o @ w[p + "o"].T
 
@@ -147,16 +168,17 @@ def latent_attention(h, w, p, m, eps):
     """Attention whose keys and values are up-projections of one normed latent per position, plus
     one turned key part that all heads share."""
     n = h.shape[0]
-    H, D, Rd, V, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+    H, D, Rd, V, R = m["heads"], m["dim"], m.get("rot_dim", 0), m["vdim"], m["kv_rank"]
+    rot = m.get("rot") or {"dims": 0, "base": 1.0}
     pos = np.arange(n, dtype=np.float64)
     q = (h @ w[p + "q"].T).reshape(n, H, D + Rd)
-    q_plain, q_rot = q[..., :D], rotate_pairs(q[..., D:], pos, m["rot"]["dims"], m["rot"]["base"])
+    q_plain, q_rot = q[..., :D], rotate_pairs(q[..., D:], pos, rot["dims"], rot["base"])
     low = h @ w[p + "dkv"].T
     c = rms_norm(low[:, :R], w[p + "dkv.norm"], eps)
-    k_rot = rotate_pairs(low[:, R:], pos, m["rot"]["dims"], m["rot"]["base"])
+    k_rot = rotate_pairs(low[:, R:], pos, rot["dims"], rot["base"])
     k_plain = (c @ w[p + "uk"].T).reshape(n, H, D)
     v = (c @ w[p + "uv"].T).reshape(n, H, V)
-    vis = window_mask(n, m["mask"]["size"])
+    vis = window_mask(n, mask_size(m))
     o = np.zeros((n, H, V))
     for a in range(H):
         s = (q_plain[:, a] @ k_plain[:, a].T + q_rot[:, a] @ k_rot.T) * m["scale"]
@@ -186,7 +208,7 @@ def layer_order(cfg):
 
 def forward(cfg, w, tokens, keep_layers=False):
     """Logits [n, vocab] of a whole sequence (and, if asked, the stream after every layer run)."""
-    eps, groups, mult = cfg["norm"]["eps"], cfg["norm"]["groups"], cfg["residual_mult"]
+    eps, groups, mult = cfg["norm"]["eps"], cfg["norm"].get("groups", 1), cfg.get("residual_mult", 1.0)
     x = w["embed"][np.asarray(tokens)]
     x0 = x.copy()
     kept = []
@@ -203,3 +225,14 @@ def forward(cfg, w, tokens, keep_layers=False):
             kept.append(x.copy())
     logits = group_norm(x, w["final.norm"], eps, groups) @ w["head"].T
     return (logits, np.stack(kept)) if keep_layers else logits
+
+
+_dirs = {}
+
+
+def forward_dir(model_dir, tokens):
+    """Logits [n, vocab] of a whole sequence through the model of a folder (read once)."""
+    if model_dir not in _dirs:
+        _dirs[model_dir] = read_model_dir(model_dir)
+    cfg, w = _dirs[model_dir]
+    return forward(cfg, w, tokens)
