@@ -180,6 +180,304 @@ talk_attention_kernel(const float* __restrict__ q, long long q_stride, const TC*
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same attention in tiles on the tensor cores (bfloat16 cache): a block takes 16 consecutive
+// queries of one request and all heads, a warp a head.  Keys come 32 at a time by absolute position
+// into shared memory, all key heads of them, 16 bytes a cp.async, the next tile on its way while one
+// is worked on.  S = Q K^T by mma.sync m16n8k16 (bfloat16 operands, 32-bit sums; a 32-bit query
+// enters as two operands, its bfloat16 rounding and what that left; the key's 1/rms, taken from
+// the staged rows, the scale and the distance penalty are applied to the accumulator).
+// First all tiles for every row's maximum and sum; then all tiles again: p = exp(s - max) / sum in
+// 32-bit, exchanged between the warps through shared memory, mixed (32-bit), packed to bfloat16 as
+// the A operand of O += P' V, whose B operand is the same staged tile read transposed.
+constexpr int TT_ROWS = 16;
+constexpr int TT_KEYS = 32;
+constexpr int TT_PPITCH = 40;       // floats between rows of a head's weights: 8-byte reads without conflicts
+constexpr int TT_MAX_HEADS = 16;
+
+__device__ __forceinline__ void tt_ldsm4(uint32_t addr, uint32_t* r) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void tt_ldsm4_t(uint32_t addr, uint32_t* r) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void tt_mma(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t tt_pack(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ void tt_cp16(uint32_t dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;       // no source bytes: the 16 destination bytes are zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ float tt_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int ND16>      // head size / 16
+__global__ void __launch_bounds__(TT_MAX_HEADS * 32)
+talk_tiles_kernel(const float* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ cache,
+                  const int* __restrict__ block_table, int bt_stride, const int* __restrict__ q_start,
+                  const int* __restrict__ kv_len, const float* __restrict__ slopes, const float* __restrict__ talk,
+                  const float* __restrict__ gate, long long gate_stride, __nv_bfloat16* __restrict__ out,
+                  long long o_stride, int H, int G, int page_size, float scale, float eps, float mult, int window,
+                  int nbuf, int n_pages, int* err) {
+  constexpr int D = ND16 * 16, DP = D + 8, CH = D / 8;
+  extern __shared__ __align__(16) unsigned char tt_smem[];
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(tt_smem);            // [2][H][16][DP]: q = high + low part
+  __nv_bfloat16* Ks = Qs + (size_t)2 * H * TT_ROWS * DP;                    // [nbuf][G][32][DP]
+  float* kinv = reinterpret_cast<float*>(Ks + (size_t)nbuf * G * TT_KEYS * DP);   // [nbuf][G][32]
+  float* Ps = kinv + (size_t)nbuf * G * TT_KEYS;                                          // [H][16][TT_PPITCH]
+  float* Ts = Ps + (size_t)H * TT_ROWS * TT_PPITCH;                         // [H][H]
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, h = tid >> 5, lane = tid & 31, nthr = blockDim.x;
+  const int c = h / (H / G);
+  for (int i = tid; i < H * H; i += nthr) Ts[i] = talk[i];
+  constexpr float LOG2E = 1.4426950408889634f;
+  const float slope2 = slopes[h] * LOG2E, scale2 = scale * LOG2E;
+  pdl_wait();
+  const int r = blockIdx.y;
+  const int t0 = q_start[r], n = q_start[r + 1] - t0, row0 = blockIdx.x * TT_ROWS;
+  if (row0 >= n) return;
+  const int rows = min(TT_ROWS, n - row0);
+  const int base_pos = kv_len[r] - n + row0, p_last = base_pos + rows - 1;
+  const int lo_blk = (window > 0 && base_pos - window + 1 > 0) ? base_pos - window + 1 : 0;
+  const int* bt = block_table + (size_t)r * bt_stride;
+  // the tile's queries, to bfloat16
+  for (int i = tid; i < H * TT_ROWS * (D / 4); i += nthr) {
+    const int d4 = i % (D / 4), row = (i / (D / 4)) % TT_ROWS, hh = i / (D / 4 * TT_ROWS);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (row < rows) v = *reinterpret_cast<const float4*>(q + (size_t)(t0 + row0 + row) * q_stride + (size_t)hh * D + d4 * 4);
+    // a 32-bit query as two bfloat16 operands: what the first leaves, the second takes
+    const float e[4] = {v.x, v.y, v.z, v.w};
+    float lo[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) lo[k] = e[k] - __bfloat162float(__float2bfloat16_rn(e[k]));
+    uint2 w, wl;
+    w.x = tt_pack(e[0], e[1]);
+    w.y = tt_pack(e[2], e[3]);
+    wl.x = tt_pack(lo[0], lo[1]);
+    wl.y = tt_pack(lo[2], lo[3]);
+    __nv_bfloat16* dst = Qs + ((size_t)hh * TT_ROWS + row) * DP + d4 * 4;
+    *reinterpret_cast<uint2*>(dst) = w;
+    *reinterpret_cast<uint2*>(dst + (size_t)H * TT_ROWS * DP) = wl;
+  }
+  const int kt_lo = lo_blk / TT_KEYS, NT = p_last / TT_KEYS - kt_lo + 1, total = 2 * NT;
+  const uint32_t ks_base = (uint32_t)__cvta_generic_to_shared(Ks);
+  auto issue = [&](int it, int buf) {
+    const int key0 = (kt_lo + it % NT) * TT_KEYS;
+    const uint32_t dst0 = ks_base + (uint32_t)buf * G * TT_KEYS * DP * 2;
+    for (int i = tid; i < G * TT_KEYS * CH; i += nthr) {
+      const int ch = i % CH, kl = (i / CH) % TT_KEYS, g = i / (CH * TT_KEYS);
+      const int j = key0 + kl;
+      bool valid = j >= lo_blk && j <= p_last;
+      const __nv_bfloat16* src = cache;
+      if (valid) {
+        const int page = bt[j / page_size];
+        valid = sglc_index_ok(page, n_pages, err);
+        if (valid) src = cache + (((size_t)page * G + g) * page_size + (size_t)(j % page_size)) * D + ch * 8;
+      }
+      tt_cp16(dst0 + (uint32_t)((g * TT_KEYS + kl) * DP + ch * 8) * 2, src, valid);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  const int g4 = lane >> 2, c2 = (lane & 3) * 2;
+  const int pos0 = base_pos + g4, pos1 = pos0 + 8;
+  const bool ok0 = g4 < rows, ok1 = g4 + 8 < rows;
+  const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(Qs) +
+                          (uint32_t)(((h * TT_ROWS + (lane & 15)) * DP + (lane >> 4) * 8) * 2);
+  const uint32_t q_low = (uint32_t)(H * TT_ROWS * DP * 2);
+  // B of S: lane -> key (lane / 16) * 8 + lane % 8 of a pair of key octets, columns ((lane / 8) % 2) * 8
+  const uint32_t kb_off = (uint32_t)(((c * TT_KEYS + (lane >> 4) * 8 + (lane & 7)) * DP + ((lane >> 3) & 1) * 8) * 2);
+  // B of O (transposed read): lane -> key ((lane / 8) % 2) * 8 + lane % 8 of 16, columns (lane / 16) * 8
+  const uint32_t vb_off = (uint32_t)(((c * TT_KEYS + ((lane >> 3) & 1) * 8 + (lane & 7)) * DP + (lane >> 4) * 8) * 2);
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f, il0 = 0.f, il1 = 0.f;
+  float o[2 * ND16][4];
+#pragma unroll
+  for (int i = 0; i < 2 * ND16; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  // every key's 1/rms of `count` staged tiles from buffer `first` on
+  auto norms = [&](int first, int count) {
+    const __nv_bfloat16* kt_rows = Ks + (size_t)first * G * TT_KEYS * DP;
+    for (int i = tid; i < count * G * TT_KEYS; i += nthr) {
+      const uint4* row = reinterpret_cast<const uint4*>(kt_rows + (size_t)i * DP);
+      float ss = 0.f;
+#pragma unroll
+      for (int ch = 0; ch < CH; ch++) {
+        const uint4 v = row[ch];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&w[e]);
+          const float x = __low2float(b), y = __high2float(b);
+          ss = fmaf(x, x, ss);
+          ss = fmaf(y, y, ss);
+        }
+      }
+      kinv[first * G * TT_KEYS + i] = 1.0f / sqrtf(ss / (float)D + eps);
+    }
+  };
+  // Where all the tiles this block visits fit the buffers, they are fetched at once and stay for
+  // the second visit; else they stream through two buffers (one, where two do not fit), twice.
+  const bool resident = NT <= nbuf;
+  if (resident) {
+    for (int it = 0; it < NT; it++) issue(it, it);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    norms(0, NT);
+    __syncthreads();
+  } else if (nbuf >= 2) {
+    issue(0, 0);
+  }
+  for (int it = 0; it < total; it++) {
+    int buf = 0;
+    if (resident) {
+      buf = it % NT;
+      if (it >= NT) __syncthreads();      // the weights of the tile before have been read
+    } else if (nbuf >= 2) {
+      buf = it & 1;
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      __syncthreads();
+      if (it + 1 < total) issue(it + 1, buf ^ 1);
+      norms(buf, 1);
+      __syncthreads();
+    } else {
+      __syncthreads();
+      issue(it, 0);
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      __syncthreads();
+      norms(0, 1);
+      __syncthreads();
+    }
+    // S: 16 queries x 32 keys of this head
+    float s[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    const uint32_t kb = ks_base + (uint32_t)buf * G * TT_KEYS * DP * 2;
+#pragma unroll
+    for (int kk = 0; kk < ND16; kk++) {
+      uint32_t a[4], al[4], b[4];
+      tt_ldsm4(q_addr + kk * 32, a);
+      tt_ldsm4(q_addr + q_low + kk * 32, al);
+#pragma unroll
+      for (int np = 0; np < 2; np++) {
+        tt_ldsm4(kb + kb_off + (uint32_t)(np * 16 * DP * 2) + kk * 32, b);
+        tt_mma(s[2 * np], al, b[0], b[1]);
+        tt_mma(s[2 * np + 1], al, b[2], b[3]);
+        tt_mma(s[2 * np], a, b[0], b[1]);
+        tt_mma(s[2 * np + 1], a, b[2], b[3]);
+      }
+    }
+    const int key0 = (kt_lo + it % NT) * TT_KEYS;
+#pragma unroll
+    for (int nt = 0; nt < 4; nt++) {
+      const float2 ki = *reinterpret_cast<const float2*>(kinv + (buf * G + c) * TT_KEYS + nt * 8 + c2);
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const int j = key0 + nt * 8 + c2 + (e & 1);
+        const int dist = ((e & 2) ? pos1 : pos0) - j;
+        const bool vis = ((e & 2) ? ok1 : ok0) && dist >= 0 && (window <= 0 || dist < window);
+        s[nt][e] = vis ? s[nt][e] * ((e & 1) ? ki.y : ki.x) * scale2 - slope2 * (float)dist : -INFINITY;
+      }
+    }
+    if (it < NT) {
+      // first visit: running maximum and sum of this thread's columns
+#pragma unroll
+      for (int hf = 0; hf < 2; hf++) {
+        float mx = hf ? m1 : m0;
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) mx = fmaxf(mx, fmaxf(s[nt][2 * hf], s[nt][2 * hf + 1]));
+        if (mx > -INFINITY) {
+          float l = (hf ? l1 : l0) * tt_exp2((hf ? m1 : m0) - mx);
+#pragma unroll
+          for (int nt = 0; nt < 4; nt++) l += tt_exp2(s[nt][2 * hf] - mx) + tt_exp2(s[nt][2 * hf + 1] - mx);
+          if (hf) { l1 = l; m1 = mx; } else { l0 = l; m0 = mx; }
+        }
+      }
+      if (it == NT - 1) {
+        // the rows' maxima and sums over the four threads that share a row
+#pragma unroll
+        for (int hf = 0; hf < 2; hf++) {
+          float mx = hf ? m1 : m0, l = hf ? l1 : l0;
+          float ma = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+          ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, 2));
+          l = mx > -INFINITY ? l * tt_exp2(mx - ma) : 0.f;
+          l += __shfl_xor_sync(0xffffffffu, l, 1);
+          l += __shfl_xor_sync(0xffffffffu, l, 2);
+          const float il = l > 0.f ? 1.0f / l : 0.f;
+          if (hf) { m1 = ma > -INFINITY ? ma : 0.f; il1 = il; } else { m0 = ma > -INFINITY ? ma : 0.f; il0 = il; }
+        }
+      }
+      continue;
+    }
+    // second visit: the weights, exchanged, mixed, applied
+    float* pw = Ps + (size_t)h * TT_ROWS * TT_PPITCH;
+#pragma unroll
+    for (int nt = 0; nt < 4; nt++) {
+      *reinterpret_cast<float2*>(pw + g4 * TT_PPITCH + nt * 8 + c2) =
+          make_float2(tt_exp2(s[nt][0] - m0) * il0, tt_exp2(s[nt][1] - m0) * il0);
+      *reinterpret_cast<float2*>(pw + (g4 + 8) * TT_PPITCH + nt * 8 + c2) =
+          make_float2(tt_exp2(s[nt][2] - m1) * il1, tt_exp2(s[nt][3] - m1) * il1);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    for (int g = 0; g < H; g++) {
+      const float w = Ts[h * H + g];
+      const float* pg = Ps + (size_t)g * TT_ROWS * TT_PPITCH;
+#pragma unroll
+      for (int nt = 0; nt < 4; nt++) {
+        const float2 a = *reinterpret_cast<const float2*>(pg + g4 * TT_PPITCH + nt * 8 + c2);
+        const float2 b = *reinterpret_cast<const float2*>(pg + (g4 + 8) * TT_PPITCH + nt * 8 + c2);
+        s[nt][0] = fmaf(w, a.x, s[nt][0]);
+        s[nt][1] = fmaf(w, a.y, s[nt][1]);
+        s[nt][2] = fmaf(w, b.x, s[nt][2]);
+        s[nt][3] = fmaf(w, b.y, s[nt][3]);
+      }
+    }
+#pragma unroll
+    for (int ks = 0; ks < 2; ks++) {
+      uint32_t a[4], b[4];
+      a[0] = tt_pack(s[2 * ks][0], s[2 * ks][1]);
+      a[1] = tt_pack(s[2 * ks][2], s[2 * ks][3]);
+      a[2] = tt_pack(s[2 * ks + 1][0], s[2 * ks + 1][1]);
+      a[3] = tt_pack(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+#pragma unroll
+      for (int dp = 0; dp < ND16; dp++) {
+        tt_ldsm4_t(kb + vb_off + (uint32_t)(ks * 16 * DP * 2) + dp * 32, b);
+        tt_mma(o[2 * dp], a, b[0], b[1]);
+        tt_mma(o[2 * dp + 1], a, b[2], b[3]);
+      }
+    }
+  }
+  // out = o * mult * sigmoid(gate)
+#pragma unroll
+  for (int hf = 0; hf < 2; hf++) {
+    const int row = g4 + 8 * hf;
+    if (row >= rows) continue;
+    const size_t t = (size_t)(t0 + row0 + row);
+    __nv_bfloat16* op = out + t * o_stride + (size_t)h * D;
+    const float* gp = gate ? gate + t * gate_stride + (size_t)h * D : nullptr;
+#pragma unroll
+    for (int nd = 0; nd < 2 * ND16; nd++) {
+      const int d = nd * 8 + c2;
+      float x = o[nd][2 * hf] * mult, y = o[nd][2 * hf + 1] * mult;
+      if (gp) {
+        x *= 1.0f / (1.0f + expf(-gp[d]));
+        y *= 1.0f / (1.0f + expf(-gp[d + 1]));
+      }
+      *reinterpret_cast<__nv_bfloat162*>(op + d) = __floats2bfloat162_rn(x, y);
+    }
+  }
+}
+
 // x: float [T][H*D queries | G*D keys | ...] as projected; wq, wk: float [D]; q_out: float [T][H*D];
 // cache: [n_pages][G][page_size][D] of cache_dtype; slots[t] = page * page_size + offset (negative: skip).
 SGLC_API int sglc_talk_prep(const float* x, long long x_stride, const float* wq, const float* wk, float eps,
@@ -232,4 +530,57 @@ SGLC_API int sglc_talk_attention(const float* q, long long q_stride, const void*
 #undef TALK_NV
 #undef TALK_GO
   return SGLC_ERR_ARGUMENT;
+}
+
+// The tiled form for a bfloat16 cache: requests' new tokens q_start[r] .. q_start[r+1]-1 end at
+// position kv_len[r] - 1; max_keys: a bound on kv_len (0: none known).  Head sizes 32, 48, 64, 96 and 128, up to 16 heads, and what fits the
+// shared memory of a block; SGLC_ERR_UNSUPPORTED otherwise (the caller then takes the kernel above).
+SGLC_API int sglc_talk_attention_tiles(const float* q, long long q_stride, const void* cache, const int* block_table,
+                                       int bt_stride, const int* q_start, const int* kv_len, const float* slopes,
+                                       const float* talk, const float* gate, long long gate_stride, void* out,
+                                       long long o_stride, int R, int max_q_len, int max_keys, int H, int G, int D,
+                                       int page_size, float scale, float eps, float mult, int window, int n_pages,
+                                       int* err,
+                                       cudaStream_t stream) {
+  if (R <= 0 || max_q_len <= 0) return SGLC_OK;
+  if (H <= 0 || G <= 0 || H % G != 0 || D <= 0 || page_size <= 0 || window < 0) return SGLC_ERR_ARGUMENT;
+  if (H > TT_MAX_HEADS || D % 16 != 0 || q_stride % 4 != 0 || o_stride % 2 != 0 || ((uintptr_t)q & 15) != 0 ||
+      ((uintptr_t)out & 3) != 0 || ((uintptr_t)cache & 15) != 0)
+    return SGLC_ERR_UNSUPPORTED;
+  auto smem_for = [&](int nbuf) {
+    const size_t DP = D + 8;
+    return (size_t)2 * H * TT_ROWS * DP * 2 + (size_t)nbuf * G * TT_KEYS * (DP * 2 + 4) +
+           (size_t)H * TT_ROWS * TT_PPITCH * 4 + (size_t)H * H * 4;
+  };
+  const size_t limit = 227 * 1024;
+  if (smem_for(1) > limit) return SGLC_ERR_UNSUPPORTED;
+  // as many tile buffers as a block's key range can span (window and queries of a tile, or the
+  // longest request), if they fit: then every tile is fetched once
+  long long span = max_keys > 0 ? max_keys : (1ll << 40);
+  const int rows = max_q_len < TT_ROWS ? max_q_len : TT_ROWS;
+  if (window > 0 && window + rows - 1 < span) span = window + rows - 1;
+  const long long want = (span + TT_KEYS - 2) / TT_KEYS + 1;
+  int nbuf = 1;
+  while (nbuf < want && smem_for(nbuf + 1) <= limit) nbuf++;
+  if (nbuf < want && nbuf > 2) nbuf = 2;      // streaming uses two
+  const size_t smem = smem_for(nbuf);
+  const dim3 grid((max_q_len + TT_ROWS - 1) / TT_ROWS, R);
+#define TT_GO(ND16)                                                                                              \
+  do {                                                                                                           \
+    if (smem > 48 * 1024)                                                                                        \
+      cudaFuncSetAttribute(talk_tiles_kernel<ND16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+    return sglc_launch(talk_tiles_kernel<ND16>, grid, dim3(H * 32), smem, stream, 1, true, q, q_stride,          \
+                       (const __nv_bfloat16*)cache, block_table, bt_stride, q_start, kv_len, slopes, talk, gate, \
+                       gate_stride, (__nv_bfloat16*)out, o_stride, H, G, page_size, scale, eps, mult, window,    \
+                       nbuf, n_pages, err);                                                                      \
+  } while (0)
+  switch (D) {
+    case 32: TT_GO(2);
+    case 48: TT_GO(3);
+    case 64: TT_GO(4);
+    case 96: TT_GO(6);
+    case 128: TT_GO(8);
+    default: return SGLC_ERR_UNSUPPORTED;
+  }
+#undef TT_GO
 }

@@ -1158,3 +1158,45 @@ def talk_attention(q, cache, block_table, token_req, positions, slopes, talk, ga
                                    ctypes.c_float(eps), ctypes.c_float(mult), int(window or 0), n_pages,
                                    _ptr(tc_error_flag(q.device)), _stream())
     _check(lib, code, f"talk_attention (head {dim}, {n_heads} heads)")
+
+
+TALK_TILES_MAX_HEADS = 16
+_TALK_UNSUPPORTED = -2
+
+
+def talk_attention_tiles(q, cache, block_table, q_start, kv_len, slopes, talk, gate, out, n_requests, max_q_len,
+                         n_heads, n_kv_heads, dim, page_size, scale, eps, mult, window, max_keys=0):
+    """talk_attention in tiles of 16 queries on the tensor cores, for a bfloat16 cache and output
+    (see attention_talk.cu): the step's requests r bring tokens q_start[r] .. q_start[r+1]-1 and
+    hold kv_len[r] positions after it (max_keys: a bound on those, or 0; it only sizes the staging:
+    where a block's whole key range fits its shared memory, every key is fetched once).  Returns False, having launched nothing, where the sizes
+    have no tiled form (head size not 32/48/64/96/128, more than 16 heads, too much shared memory,
+    rows not aligned): the caller then takes talk_attention."""
+    if cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or n_heads > TALK_TILES_MAX_HEADS \
+            or dim not in (32, 48, 64, 96, 128):
+        return False
+    _need_cuda(q, cache, block_table, q_start, kv_len, slopes, talk, gate, out)
+    _f32_rows(q, "talk_attention_tiles: q", n_heads * dim)
+    for t, nm in ((block_table, "block_table"), (q_start, "q_start"), (kv_len, "kv_len")):
+        _i32(t, nm)
+    if gate is not None:
+        _f32_rows(gate, "talk_attention_tiles: gate", n_heads * dim)
+    n_pages = cache.shape[0]
+    if slopes.dtype != torch.float32 or slopes.numel() != n_heads or talk.dtype != torch.float32 \
+            or talk.numel() != n_heads * n_heads or not talk.is_contiguous():
+        raise KernelError("talk_attention_tiles: slopes float32 [H], talk float32 [H, H]")
+    if out.shape[1] != n_heads * dim or out.stride(1) != 1 or not cache.is_contiguous() \
+            or cache.numel() != n_pages * n_kv_heads * page_size * dim:
+        raise KernelError("talk_attention_tiles: out [T, H*dim]; the cache keeps one row per position and key head")
+    lib = build.load("attention_talk")
+    code = lib.sglc_talk_attention_tiles(
+        _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(cache), _ptr(block_table), block_table.stride(0), _ptr(q_start),
+        _ptr(kv_len), _ptr(slopes), _ptr(talk), _ptr(gate), ctypes.c_longlong(gate.stride(0) if gate is not None else 0),
+        _ptr(out), ctypes.c_longlong(out.stride(0)), int(n_requests), int(max_q_len), int(max_keys or 0), int(n_heads),
+        int(n_kv_heads),
+        int(dim), int(page_size), ctypes.c_float(scale), ctypes.c_float(eps), ctypes.c_float(mult), int(window or 0),
+        n_pages, _ptr(tc_error_flag(q.device)), _stream())
+    if code == _TALK_UNSUPPORTED:
+        return False
+    _check(lib, code, f"talk_attention_tiles (head {dim}, {n_heads} heads)")
+    return True

@@ -317,9 +317,15 @@ class TalkingHeadsAttention(Part):
         q = ctx.alloc((T, H * D), torch.float32)
         ops.talk_prep(pre, self.q_norm, self.k_norm, eps, q, cache.tensor, grp.slots, H, G, D, grp.page_size)
         o = ctx.alloc((T, H * D), self.rt.act_dtype)
-        ops.talk_attention(q, cache.tensor, grp.block_table, ctx.token_req, ctx.positions, self.slopes, self.talk,
-                           ctx.columns(pre, (H + G) * D, (2 * H + G) * D), o, H, G, D, grp.page_size,
-                           float(p["scale"]), eps, float(p.get("out_mult", 1.0)), p.get("window"))
+        gate = ctx.columns(pre, (H + G) * D, (2 * H + G) * D)
+        scale, mult = float(p["scale"]), float(p.get("out_mult", 1.0))
+        # bfloat16: tiles of 16 queries of a request on the tensor cores (a single token is a tile
+        # of one row); 32-bit, and sizes without a tiled form: a block a token
+        if self.rt.dtype != "bfloat16" or not ops.talk_attention_tiles(
+                q, cache.tensor, grp.block_table, ctx.q_start, ctx.kv_len, self.slopes, self.talk, gate, o, ctx.R,
+                ctx.max_q_len, H, G, D, grp.page_size, scale, eps, mult, p.get("window"), max_keys=ctx.max_keys):
+            ops.talk_attention(q, cache.tensor, grp.block_table, ctx.token_req, ctx.positions, self.slopes, self.talk,
+                               gate, o, H, G, D, grp.page_size, scale, eps, mult, p.get("window"))
         return self.out.forward(ctx, o, out=out, residual=residual)
 
 

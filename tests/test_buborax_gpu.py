@@ -170,10 +170,26 @@ def _talk_case(rng, n, H, G, D, far=()):
                                               (4, 4, 64, 130, 16), (1, 1, 7, 3, 8), (6, 2, 24, 300, 16)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_talking_heads_attention_windows_far_keys_and_portions(H, G, D, window, page, dtype):
+    _talk_in_cuts(H, G, D, window, page, dtype, tiled=False)
+
+
+@pytest.mark.parametrize("H,G,D,window,page", [(4, 2, 32, 37, 16), (2, 1, 64, None, 16), (3, 3, 48, 8, 8),
+                                              (8, 2, 128, 130, 32), (1, 1, 32, 3, 8), (6, 2, 96, 300, 16),
+                                              (16, 4, 32, 33, 16), (5, 5, 64, 32, 24), (2, 2, 64, 16, 16)])
+@pytest.mark.parametrize("max_keys", [None, 1 << 20])
+def test_talking_heads_attention_in_tiles(H, G, D, window, page, max_keys):
+    """max_keys None: the longest request's length, so that every key is staged once where that fits
+    (and twice through two buffers where it does not); a bound far off: always through two buffers
+    where there is no window."""
+    _talk_in_cuts(H, G, D, window, page, torch.bfloat16, tiled=True, max_keys=max_keys)
+
+
+def _talk_in_cuts(H, G, D, window, page, dtype, tiled, max_keys=None):
     """Two requests over shuffled pages, whole, then in portions with single tokens at the end.  In the
     first request the key just inside the window of the last query, the key just outside the window
     of the query before it (and, without a window, a key hundreds back) stand out: a window one token
-    off, or a lost key, changes the result by its own size."""
+    off, or a lost key, changes the result by its own size.  tiled: the tensor-core form, which
+    takes the requests' first rows and lengths in place of a request and a position per token."""
     from sglang_c_b200.csrc import ops
     rng = np.random.default_rng(H * 100 + D)
     lens = [333, 70]
@@ -189,7 +205,7 @@ def test_talking_heads_attention_windows_far_keys_and_portions(H, G, D, window, 
     if window is not None:             # the stand-out keys matter: one token off is another result
         assert np.abs(plain(cases[0], window + 1)[last - 1] - plain(cases[0], window)[last - 1]).max() > 1.0
         assert np.abs(plain(cases[0], window - 1)[last] - plain(cases[0], window)[last]).max() > 1.0
-    n_pages = 40 if page == 16 else 80
+    n_pages = {16: 40, 8: 80}.get(page, 30)
     blocks = [(n + page - 1) // page for n in lens]
     perm = rng.permutation(n_pages)
     tables = np.zeros((2, max(blocks)), dtype=np.int64)
@@ -215,8 +231,16 @@ def test_talking_heads_attention_windows_far_keys_and_portions(H, G, D, window, 
             qn = torch.zeros((T, H * D), device=DEV)
             ops.talk_prep(x, dev(gq), dev(gk), 1e-6, qn, cache, i32(slots), H, G, D, page)
             out = torch.zeros((T, H * D), dtype=dtype, device=DEV)
-            ops.talk_attention(qn, cache, i32(bt), i32(token_req), i32(pos), slopes, dev(talk.reshape(-1)), gate, out,
-                               H, G, D, page, scale, 1e-6, mult, window)
+            if tiled:
+                counts = [hi - lo for _, lo, hi in live]
+                q_start = np.concatenate([[0], np.cumsum(counts)])
+                assert ops.talk_attention_tiles(qn, cache, i32(bt), i32(q_start), i32([hi for _, _, hi in live]),
+                                                slopes, dev(talk.reshape(-1)), gate, out, len(live), max(counts), H,
+                                                G, D, page, scale, 1e-6, mult, window,
+                                                max_keys=max_keys if max_keys else max(hi for _, _, hi in live))
+            else:
+                ops.talk_attention(qn, cache, i32(bt), i32(token_req), i32(pos), slopes, dev(talk.reshape(-1)), gate,
+                                   out, H, G, D, page, scale, 1e-6, mult, window)
             o = f64(out)
             at = 0
             for r, lo, hi in live:
