@@ -222,6 +222,27 @@ __device__ __forceinline__ float tt_exp2(float x) {
   return y;
 }
 
+// Blocks of one grid.z column form a cluster and share a tile's keys between them (below).
+__device__ __forceinline__ uint32_t tt_peer(const void* local, uint32_t rank) {
+  uint32_t raddr;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+  return raddr;
+}
+__device__ __forceinline__ float2 tt_peer_ld2(uint32_t raddr) {
+  float2 v;
+  asm volatile("ld.shared::cluster.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(raddr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void tt_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// gridDim.z = S blocks (a cluster, S > 1) divide the key tiles of one tile of queries: each visits
+// its share for the maxima and sums, the S pairs per (head, row) are merged through the cluster's
+// shared memory, each forms mixed weights and a partial result over its share, and block 0 adds
+// the partial results (the result is linear in the normalised weights) and writes.  This is the
+// form for few tiles of queries (decoding), where one block a request leaves the GPU idle.
 template <int ND16>      // head size / 16
 __global__ void __launch_bounds__(TT_MAX_HEADS * 32)
 talk_tiles_kernel(const float* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ cache,
@@ -237,6 +258,9 @@ talk_tiles_kernel(const float* __restrict__ q, long long q_stride, const __nv_bf
   float* kinv = reinterpret_cast<float*>(Ks + (size_t)nbuf * G * TT_KEYS * DP);   // [nbuf][G][32]
   float* Ps = kinv + (size_t)nbuf * G * TT_KEYS;                                          // [H][16][TT_PPITCH]
   float* Ts = Ps + (size_t)H * TT_ROWS * TT_PPITCH;                         // [H][H]
+  float* stat = Ts + ((H * H + 1) & ~1);                                    // [H][16][2]: (max, sum), S > 1
+  float* Os = stat + (size_t)H * TT_ROWS * 2;                               // [H][rows][D]: partial result, S > 1
+  const int S = gridDim.z, z = blockIdx.z;
   pdl_launch_dependents();
   const int tid = threadIdx.x, h = tid >> 5, lane = tid & 31, nthr = blockDim.x;
   const int c = h / (H / G);
@@ -270,7 +294,9 @@ talk_tiles_kernel(const float* __restrict__ q, long long q_stride, const __nv_bf
     *reinterpret_cast<uint2*>(dst) = w;
     *reinterpret_cast<uint2*>(dst + (size_t)H * TT_ROWS * DP) = wl;
   }
-  const int kt_lo = lo_blk / TT_KEYS, NT = p_last / TT_KEYS - kt_lo + 1, total = 2 * NT;
+  // this block's share of the key tiles (none, where there are fewer tiles than blocks)
+  const int kt_all = lo_blk / TT_KEYS, nt_all = p_last / TT_KEYS - kt_all + 1;
+  const int kt_lo = kt_all + nt_all * z / S, NT = kt_all + nt_all * (z + 1) / S - kt_lo, total = 2 * NT;
   const uint32_t ks_base = (uint32_t)__cvta_generic_to_shared(Ks);
   auto issue = [&](int it, int buf) {
     const int key0 = (kt_lo + it % NT) * TT_KEYS;
@@ -324,6 +350,45 @@ talk_tiles_kernel(const float* __restrict__ q, long long q_stride, const __nv_bf
       kinv[first * G * TT_KEYS + i] = 1.0f / sqrtf(ss / (float)D + eps);
     }
   };
+  // after the first visit: the rows' maxima and sums over the four threads that share a row, and
+  // over the blocks of the cluster
+  auto finish_first = [&]() {
+#pragma unroll
+    for (int hf = 0; hf < 2; hf++) {
+      float mx = hf ? m1 : m0, l = hf ? l1 : l0;
+      float ma = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, 2));
+      l = mx > -INFINITY ? l * tt_exp2(mx - ma) : 0.f;
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      if (hf) { m1 = ma; l1 = l; } else { m0 = ma; l0 = l; }
+    }
+    if (S > 1) {
+      if ((lane & 3) == 0) {
+        *reinterpret_cast<float2*>(stat + (h * TT_ROWS + g4) * 2) = make_float2(m0, l0);
+        *reinterpret_cast<float2*>(stat + (h * TT_ROWS + g4 + 8) * 2) = make_float2(m1, l1);
+      }
+      tt_cluster_sync();
+      float ma0 = -INFINITY, ma1 = -INFINITY;
+      for (int zz = 0; zz < S; zz++) {
+        ma0 = fmaxf(ma0, tt_peer_ld2(tt_peer(stat + (h * TT_ROWS + g4) * 2, zz)).x);
+        ma1 = fmaxf(ma1, tt_peer_ld2(tt_peer(stat + (h * TT_ROWS + g4 + 8) * 2, zz)).x);
+      }
+      float s0 = 0.f, s1 = 0.f;
+      for (int zz = 0; zz < S; zz++) {
+        const float2 a = tt_peer_ld2(tt_peer(stat + (h * TT_ROWS + g4) * 2, zz));
+        const float2 b = tt_peer_ld2(tt_peer(stat + (h * TT_ROWS + g4 + 8) * 2, zz));
+        if (a.x > -INFINITY) s0 = fmaf(a.y, tt_exp2(a.x - ma0), s0);
+        if (b.x > -INFINITY) s1 = fmaf(b.y, tt_exp2(b.x - ma1), s1);
+      }
+      m0 = ma0; l0 = s0; m1 = ma1; l1 = s1;
+    }
+    il0 = l0 > 0.f ? 1.0f / l0 : 0.f;
+    il1 = l1 > 0.f ? 1.0f / l1 : 0.f;
+    if (!(m0 > -INFINITY)) m0 = 0.f;
+    if (!(m1 > -INFINITY)) m1 = 0.f;
+  };
+  if (NT == 0) finish_first();
   // Where all the tiles this block visits fit the buffers, they are fetched at once and stay for
   // the second visit; else they stream through two buffers (one, where two do not fit), twice.
   const bool resident = NT <= nbuf;
@@ -401,20 +466,7 @@ talk_tiles_kernel(const float* __restrict__ q, long long q_stride, const __nv_bf
           if (hf) { l1 = l; m1 = mx; } else { l0 = l; m0 = mx; }
         }
       }
-      if (it == NT - 1) {
-        // the rows' maxima and sums over the four threads that share a row
-#pragma unroll
-        for (int hf = 0; hf < 2; hf++) {
-          float mx = hf ? m1 : m0, l = hf ? l1 : l0;
-          float ma = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-          ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, 2));
-          l = mx > -INFINITY ? l * tt_exp2(mx - ma) : 0.f;
-          l += __shfl_xor_sync(0xffffffffu, l, 1);
-          l += __shfl_xor_sync(0xffffffffu, l, 2);
-          const float il = l > 0.f ? 1.0f / l : 0.f;
-          if (hf) { m1 = ma > -INFINITY ? ma : 0.f; il1 = il; } else { m0 = ma > -INFINITY ? ma : 0.f; il0 = il; }
-        }
-      }
+      if (it == NT - 1) finish_first();
       continue;
     }
     // second visit: the weights, exchanged, mixed, applied
@@ -456,6 +508,35 @@ talk_tiles_kernel(const float* __restrict__ q, long long q_stride, const __nv_bf
         tt_mma(o[2 * dp + 1], a, b[2], b[3]);
       }
     }
+  }
+  if (S > 1) {
+    // the blocks' partial results, added by block 0
+#pragma unroll
+    for (int hf = 0; hf < 2; hf++) {
+      const int row = g4 + 8 * hf;
+      if (row >= rows) continue;
+#pragma unroll
+      for (int nd = 0; nd < 2 * ND16; nd++)
+        *reinterpret_cast<float2*>(Os + ((size_t)h * rows + row) * D + nd * 8 + c2) = make_float2(o[nd][2 * hf], o[nd][2 * hf + 1]);
+    }
+    tt_cluster_sync();
+    if (z == 0) {
+      for (int zz = 1; zz < S; zz++) {
+#pragma unroll
+        for (int hf = 0; hf < 2; hf++) {
+          const int row = g4 + 8 * hf;
+          if (row >= rows) continue;
+#pragma unroll
+          for (int nd = 0; nd < 2 * ND16; nd++) {
+            const float2 v = tt_peer_ld2(tt_peer(Os + ((size_t)h * rows + row) * D + nd * 8 + c2, zz));
+            o[nd][2 * hf] += v.x;
+            o[nd][2 * hf + 1] += v.y;
+          }
+        }
+      }
+    }
+    tt_cluster_sync();      // no block leaves while block 0 reads from it
+    if (z != 0) return;
   }
   // out = o * mult * sigmoid(gate)
 #pragma unroll
@@ -532,6 +613,11 @@ SGLC_API int sglc_talk_attention(const float* q, long long q_stride, const void*
   return SGLC_ERR_ARGUMENT;
 }
 
+// Tuning hook: 0 keeps one block a tile of queries whatever the grid (default 1: clusters where the
+// grid is small).
+static int g_tt_split = 1;
+SGLC_API void sglc_talk_tiles_set_split(int on) { g_tt_split = on; }
+
 // The tiled form for a bfloat16 cache: requests' new tokens q_start[r] .. q_start[r+1]-1 end at
 // position kv_len[r] - 1; max_keys: a bound on kv_len (0: none known).  Head sizes 32, 48, 64, 96 and 128, up to 16 heads, and what fits the
 // shared memory of a block; SGLC_ERR_UNSUPPORTED otherwise (the caller then takes the kernel above).
@@ -547,29 +633,40 @@ SGLC_API int sglc_talk_attention_tiles(const float* q, long long q_stride, const
   if (H > TT_MAX_HEADS || D % 16 != 0 || q_stride % 4 != 0 || o_stride % 2 != 0 || ((uintptr_t)q & 15) != 0 ||
       ((uintptr_t)out & 3) != 0 || ((uintptr_t)cache & 15) != 0)
     return SGLC_ERR_UNSUPPORTED;
-  auto smem_for = [&](int nbuf) {
-    const size_t DP = D + 8;
-    return (size_t)2 * H * TT_ROWS * DP * 2 + (size_t)nbuf * G * TT_KEYS * (DP * 2 + 4) +
-           (size_t)H * TT_ROWS * TT_PPITCH * 4 + (size_t)H * H * 4;
-  };
-  const size_t limit = 227 * 1024;
-  if (smem_for(1) > limit) return SGLC_ERR_UNSUPPORTED;
+  const int rows = max_q_len < TT_ROWS ? max_q_len : TT_ROWS;
+  const dim3 tiles((max_q_len + TT_ROWS - 1) / TT_ROWS, R);
   // as many tile buffers as a block's key range can span (window and queries of a tile, or the
   // longest request), if they fit: then every tile is fetched once
   long long span = max_keys > 0 ? max_keys : (1ll << 40);
-  const int rows = max_q_len < TT_ROWS ? max_q_len : TT_ROWS;
   if (window > 0 && window + rows - 1 < span) span = window + rows - 1;
-  const long long want = (span + TT_KEYS - 2) / TT_KEYS + 1;
+  const long long span_tiles = (span + TT_KEYS - 2) / TT_KEYS + 1;
+  // few tiles of queries: a cluster of up to 8 blocks shares the key tiles of each
+  int split = 1;
+  const long long blocks = (long long)tiles.x * tiles.y;
+  if (g_tt_split && blocks * 2 <= 128 && span_tiles >= 2) {
+    split = (int)(128 / blocks < 8 ? 128 / blocks : 8);
+    if (split > span_tiles) split = (int)span_tiles;
+  }
+  auto smem_for = [&](int nbuf, int S) {
+    const size_t DP = D + 8;
+    return (size_t)2 * H * TT_ROWS * DP * 2 + (size_t)nbuf * G * TT_KEYS * (DP * 2 + 4) +
+           (size_t)H * TT_ROWS * TT_PPITCH * 4 + (size_t)((H * H + 1) & ~1) * 4 +
+           (S > 1 ? (size_t)H * TT_ROWS * 2 * 4 + (size_t)H * rows * D * 4 : 0);
+  };
+  const size_t limit = 227 * 1024;
+  if (split > 1 && smem_for(1, split) > limit) split = 1;
+  if (smem_for(1, split) > limit) return SGLC_ERR_UNSUPPORTED;
+  const long long want = (span_tiles + split - 1) / split;
   int nbuf = 1;
-  while (nbuf < want && smem_for(nbuf + 1) <= limit) nbuf++;
+  while (nbuf < want && smem_for(nbuf + 1, split) <= limit) nbuf++;
   if (nbuf < want && nbuf > 2) nbuf = 2;      // streaming uses two
-  const size_t smem = smem_for(nbuf);
-  const dim3 grid((max_q_len + TT_ROWS - 1) / TT_ROWS, R);
+  const size_t smem = smem_for(nbuf, split);
+  const dim3 grid(tiles.x, tiles.y, split);
 #define TT_GO(ND16)                                                                                              \
   do {                                                                                                           \
     if (smem > 48 * 1024)                                                                                        \
       cudaFuncSetAttribute(talk_tiles_kernel<ND16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
-    return sglc_launch(talk_tiles_kernel<ND16>, grid, dim3(H * 32), smem, stream, 1, true, q, q_stride,          \
+    return sglc_launch(talk_tiles_kernel<ND16>, grid, dim3(H * 32), smem, stream, split, true, q, q_stride,      \
                        (const __nv_bfloat16*)cache, block_table, bt_stride, q_start, kv_len, slopes, talk, gate, \
                        gate_stride, (__nv_bfloat16*)out, o_stride, H, G, page_size, scale, eps, mult, window,    \
                        nbuf, n_pages, err);                                                                      \

@@ -79,10 +79,20 @@ def test_norm_of_each_head_without_a_gate():
 
 
 @pytest.mark.parametrize("H,D,V", [(4, 16, 24), (2, 64, 80), (3, 7, 5), (1, 200, 33), (2, 128, 1), (1, 48, 32)])
-def test_row_gated_state_in_portions(H, D, V):
+@pytest.mark.parametrize("general", [False, True])
+def test_row_gated_state_in_portions(H, D, V, general):
     """Three requests of unequal lengths in shuffled slots, whole and cut into portions (the state is
-    carried through its slot), with lower bounds close to one so that the first tokens still count."""
+    carried through its slot), with lower bounds close to one so that the first tokens still count.
+    general: on the kernel that all forms share, in place of the one for forms without feedback."""
     from sglang_c_b200.csrc import ops
+    ops.set_kernel_choice(state_without_feedback=not general)
+    try:
+        _row_gated_in_portions(ops, H, D, V)
+    finally:
+        ops.set_kernel_choice(state_without_feedback=True)
+
+
+def _row_gated_in_portions(ops, H, D, V):
     rng = np.random.default_rng(H * 1000 + D)
     lens = [45, 1, 18]
     lower = 0.97 + 0.029 * rng.random(H * D)
@@ -177,11 +187,19 @@ def test_talking_heads_attention_windows_far_keys_and_portions(H, G, D, window, 
                                               (8, 2, 128, 130, 32), (1, 1, 32, 3, 8), (6, 2, 96, 300, 16),
                                               (16, 4, 32, 33, 16), (5, 5, 64, 32, 24), (2, 2, 64, 16, 16)])
 @pytest.mark.parametrize("max_keys", [None, 1 << 20])
-def test_talking_heads_attention_in_tiles(H, G, D, window, page, max_keys):
+@pytest.mark.parametrize("split", [True, False])
+def test_talking_heads_attention_in_tiles(H, G, D, window, page, max_keys, split):
     """max_keys None: the longest request's length, so that every key is staged once where that fits
     (and twice through two buffers where it does not); a bound far off: always through two buffers
-    where there is no window."""
-    _talk_in_cuts(H, G, D, window, page, torch.bfloat16, tiled=True, max_keys=max_keys)
+    where there is no window.  split: small grids divide a tile's keys over a cluster of blocks (some
+    of which get no keys where the window is short or the request has just begun); without it every
+    tile of queries is one block's."""
+    from sglang_c_b200.csrc import ops
+    ops.set_kernel_choice(talk_key_split=split)
+    try:
+        _talk_in_cuts(H, G, D, window, page, torch.bfloat16, tiled=True, max_keys=max_keys)
+    finally:
+        ops.set_kernel_choice(talk_key_split=True)
 
 
 def _talk_in_cuts(H, G, D, window, page, dtype, tiled, max_keys=None):
