@@ -252,169 +252,6 @@ matrix_state_kernel(MsArgs p) {
   }
 }
 
-// The forms without feedback (decay, row-gated): a token's write does not read the state, so the
-// only chain from token to token is one multiply-add per entry, and the read-outs' sums over lanes
-// wait for nothing.  A lane keeps 8 rows of CPL neighbouring columns (D <= 8 L), so what it takes
-// out of shared memory per token (8 entries of q, 8 of the write's shares) serves 8 CPL entries of
-// state; a warp has 32 / L * CPL columns, four warps a block share the staged tokens.
-template <int L, int CPL, int MODE>
-__global__ void __launch_bounds__(128)
-matrix_state_open_kernel(MsArgs p) {
-  constexpr int PER = 8, NW = 4, THREADS = 32 * NW, DP = PER * L, WCOLS = 32 / L * CPL, COLS = WCOLS * NW;
-  constexpr int LP = PER + 4, SP = L * LP;
-  constexpr int BATCH = L <= 8 ? 16 : (L == 16 ? 8 : 4);          // tokens staged at a time (two halves in 48 KB)
-  constexpr int NK = (BATCH * DP + THREADS - 1) / THREADS, NV = (BATCH * COLS + THREADS - 1) / THREADS;
-  __shared__ __align__(16) float ks[2][BATCH * SP], qs[2][BATCH * SP];
-  __shared__ float vs[2][BATCH * COLS];
-  pdl_launch_dependents();
-  const int r = blockIdx.x, h = blockIdx.y, g = h / (p.H / p.G);
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, sub = lane % L, wcol = warp * WCOLS + lane / L * CPL;
-  const int col0 = blockIdx.z * COLS + wcol;
-  pdl_wait();
-  const int t0 = p.q_start[r], t1 = p.q_start[r + 1];
-  const int slot = p.state_slots[r];
-  if (t1 <= t0 || !sglc_index_ok(slot, p.n_slots, p.err)) return;
-  float* sp = p.state + ((size_t)slot * p.H + h) * p.D * p.V;
-  float S[CPL][PER];
-#pragma unroll
-  for (int c = 0; c < CPL; c++)
-#pragma unroll
-    for (int e = 0; e < PER; e++) {
-      const int i = sub * PER + e;
-      S[c][e] = (col0 + c < p.V && i < p.D) ? sp[(size_t)i * p.V + col0 + c] : 0.0f;
-    }
-  const float hd = MODE == MS_DECAY ? p.head_decay[h] : 0.0f;
-  float* out_row = p.out + (size_t)h * p.V + col0;
-  float rk[NK], rq[NK], rv[NV];
-  auto fetch = [&](int tb) {
-#pragma unroll
-    for (int n = 0; n < NK; n++) {
-      const int x = tid + n * THREADS, b = x / DP, i = x % DP;
-      const bool in = x < BATCH * DP && tb + b < t1 && i < p.D;
-      rk[n] = in ? __ldg(p.k + (size_t)(tb + b) * p.k_stride + (size_t)g * p.D + i) : 0.0f;
-      rq[n] = in ? __ldg(p.q + (size_t)(tb + b) * p.q_stride + (size_t)g * p.D + i) : 0.0f;
-    }
-#pragma unroll
-    for (int n = 0; n < NV; n++) {
-      const int x = tid + n * THREADS, b = x / COLS, c = blockIdx.z * COLS + x % COLS;
-      rv[n] = (x < BATCH * COLS && tb + b < t1 && c < p.V)
-                  ? __ldg(p.v + (size_t)(tb + b) * p.v_stride + (size_t)h * p.V + c) : 0.0f;
-    }
-  };
-  auto stage = [&](int buf) {
-#pragma unroll
-    for (int n = 0; n < NK; n++) {
-      const int x = tid + n * THREADS;
-      if (x < BATCH * DP) {
-        const int b = x / DP, i = x % DP, at = b * SP + i / PER * LP + i % PER;
-        if (MODE == MS_ROWGATE) {
-          // 1 - f = (1 - l) sigmoid(-x), formed without f (rows beyond the key size take in nothing)
-          const float lo = i < p.D ? __ldg(p.lower + (size_t)g * p.D + i) : 1.0f;
-          ks[buf][at] = (1.0f - lo) * (1.0f / (1.0f + expf(rk[n])));
-        } else {
-          ks[buf][at] = p.silu_in ? ms_silu(rk[n]) : rk[n];
-        }
-        qs[buf][at] = p.silu_in ? ms_silu(rq[n]) : rq[n];
-      }
-    }
-#pragma unroll
-    for (int n = 0; n < NV; n++) {
-      const int x = tid + n * THREADS;
-      if (x < BATCH * COLS) vs[buf][x] = (p.silu_in && MODE != MS_ROWGATE) ? ms_silu(rv[n]) : rv[n];
-    }
-  };
-  fetch(t0);
-  int buf = 0;
-  for (int tb = t0; tb < t1; tb += BATCH, buf ^= 1) {
-    const int nb = min(BATCH, t1 - tb);
-    stage(buf);
-    __syncthreads();
-    if (tb + BATCH < t1) fetch(tb + BATCH);
-    // one token: the lane's entries move on, and its share of the CPL read-outs
-    auto token = [&](int b, float (&o)[CPL]) {
-      const float4* kr = reinterpret_cast<const float4*>(ks[buf] + b * SP + sub * LP);
-      const float4* qr = reinterpret_cast<const float4*>(qs[buf] + b * SP + sub * LP);
-      const float4 ka = kr[0], kb = kr[1], qa = qr[0], qb = qr[1];
-      const float kk[PER] = {ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w};
-      const float qq[PER] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-#pragma unroll
-      for (int c = 0; c < CPL; c++) {
-        const float vv = vs[buf][b * COLS + wcol + c];
-        float oa = 0.0f, ob = 0.0f;
-#pragma unroll
-        for (int e = 0; e < PER; e += 2) {
-          if (MODE == MS_ROWGATE) {
-            S[c][e] = fmaf(kk[e], vv - S[c][e], S[c][e]);
-            S[c][e + 1] = fmaf(kk[e + 1], vv - S[c][e + 1], S[c][e + 1]);
-          } else {
-            S[c][e] = fmaf(kk[e], vv, hd * S[c][e]);
-            S[c][e + 1] = fmaf(kk[e + 1], vv, hd * S[c][e + 1]);
-          }
-          oa = fmaf(S[c][e], qq[e], oa);
-          ob = fmaf(S[c][e + 1], qq[e + 1], ob);
-        }
-        o[c] = oa + ob;
-      }
-    };
-    auto finish = [&](int b, float (&o)[CPL]) {
-#pragma unroll
-      for (int c = 0; c < CPL; c++) {
-        float x = o[c];
-#pragma unroll
-        for (int m = 1; m < L; m <<= 1) x += __shfl_xor_sync(0xffffffffu, x, m);
-        if (sub == 0 && col0 + c < p.V)
-          asm volatile("st.global.f32 [%0], %1;" ::"l"(out_row + (size_t)(tb + b) * p.out_stride + c), "f"(x));
-      }
-    };
-    int b0 = 0;
-    for (; b0 + MS_UNROLL <= nb; b0 += MS_UNROLL) {
-      float o[MS_UNROLL][CPL];
-#pragma unroll
-      for (int b = 0; b < MS_UNROLL; b++) token(b0 + b, o[b]);
-#pragma unroll
-      for (int b = 0; b < MS_UNROLL; b++) finish(b0 + b, o[b]);
-    }
-    for (; b0 < nb; b0++) {
-      float o[CPL];
-      token(b0, o);
-      finish(b0, o);
-    }
-  }
-#pragma unroll
-  for (int c = 0; c < CPL; c++)
-#pragma unroll
-    for (int e = 0; e < PER; e++) {
-      const int i = sub * PER + e;
-      if (col0 + c < p.V && i < p.D) sp[(size_t)i * p.V + col0 + c] = S[c][e];
-    }
-}
-
-// Tuning hook: 1 (default) sends the forms without feedback to matrix_state_open_kernel; 0 keeps
-// them on the general kernel.
-static int g_ms_open = 1;
-SGLC_API void sglc_matrix_state_set_open(int on) { g_ms_open = on; }
-
-template <int MODE>
-static int ms_open_launch(const MsArgs& p, cudaStream_t stream) {
-  int L = 1;
-  while (8 * L < p.D) L <<= 1;
-  // two columns a lane where that still leaves every scheduler a warp or more
-  const long long warps2 = (long long)p.R * p.H * ((p.V + 32 / L * 2 - 1) / (32 / L * 2));
-  const int cpl = warps2 >= 148LL * 4 ? 2 : 1;
-  const int cols = 32 / L * cpl * 4, zb = (p.V + cols - 1) / cols;
-  if (zb > 65535) return SGLC_ERR_UNSUPPORTED;
-  const dim3 grid(p.R, p.H, zb);
-#define MSO_CASE(LL)                                                                                          \
-  case LL:                                                                                                    \
-    return cpl == 2 ? sglc_launch(matrix_state_open_kernel<LL, 2, MODE>, grid, dim3(128), 0, stream, 1, true, p) \
-                    : sglc_launch(matrix_state_open_kernel<LL, 1, MODE>, grid, dim3(128), 0, stream, 1, true, p);
-  switch (L) {
-    MSO_CASE(1) MSO_CASE(2) MSO_CASE(4) MSO_CASE(8) MSO_CASE(16) MSO_CASE(32)
-  }
-#undef MSO_CASE
-  return SGLC_ERR_UNSUPPORTED;
-}
-
 template <int PER, int MODE, int NW>
 static int ms_launch(const MsArgs& p, int L, dim3 grid, cudaStream_t stream) {
 #define MS_CASE(LL)                                                                                         \
@@ -472,7 +309,6 @@ SGLC_API int sglc_matrix_state_ext(int mode, const float* q, long long q_stride,
   } while (0)
   if (mode == MS_DECAY) {
     if (!head_decay) return SGLC_ERR_ARGUMENT;
-    if (g_ms_open && D <= 256) return ms_open_launch<MS_DECAY>(p, stream);
     MS_GO(MS_DECAY);
   }
   if (mode == MS_DELTA) {
@@ -481,7 +317,6 @@ SGLC_API int sglc_matrix_state_ext(int mode, const float* q, long long q_stride,
   }
   if (mode == MS_ROWGATE) {
     if (!lower || G != H) return SGLC_ERR_ARGUMENT;
-    if (g_ms_open && D <= 256) return ms_open_launch<MS_ROWGATE>(p, stream);
     MS_GO(MS_ROWGATE);
   }
   return SGLC_ERR_ARGUMENT;

@@ -820,13 +820,9 @@ def set_pdl(on):
         build.load(name).sglc_set_pdl(1 if on else 0)
 
 
-def set_kernel_choice(*, state_without_feedback=None, talk_key_split=None):
-    """Tuning and test hooks (both on by default).  state_without_feedback: the decay and row-gated
-    forms of matrix_state on the kernel that keeps eight rows of several columns a lane (off: the
-    general kernel).  talk_key_split: talk_attention_tiles divides a tile's keys over a cluster of
-    blocks where the grid is small (off: always one block a tile of queries)."""
-    if state_without_feedback is not None:
-        build.load("matrix_state").sglc_matrix_state_set_open(1 if state_without_feedback else 0)
+def set_kernel_choice(*, talk_key_split=None):
+    """Tuning and test hook.  talk_key_split (on by default): talk_attention_tiles divides a tile's
+    keys over a cluster of blocks where the grid is small (off: always one block a tile of queries)."""
     if talk_key_split is not None:
         build.load("attention_talk").sglc_talk_tiles_set_split(1 if talk_key_split else 0)
 

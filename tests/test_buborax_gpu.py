@@ -79,17 +79,11 @@ def test_norm_of_each_head_without_a_gate():
 
 
 @pytest.mark.parametrize("H,D,V", [(4, 16, 24), (2, 64, 80), (3, 7, 5), (1, 200, 33), (2, 128, 1), (1, 48, 32)])
-@pytest.mark.parametrize("general", [False, True])
-def test_row_gated_state_in_portions(H, D, V, general):
+def test_row_gated_state_in_portions(H, D, V):
     """Three requests of unequal lengths in shuffled slots, whole and cut into portions (the state is
-    carried through its slot), with lower bounds close to one so that the first tokens still count.
-    general: on the kernel that all forms share, in place of the one for forms without feedback."""
+    carried through its slot), with lower bounds close to one so that the first tokens still count."""
     from sglang_c_b200.csrc import ops
-    ops.set_kernel_choice(state_without_feedback=not general)
-    try:
-        _row_gated_in_portions(ops, H, D, V)
-    finally:
-        ops.set_kernel_choice(state_without_feedback=True)
+    _row_gated_in_portions(ops, H, D, V)
 
 
 def _row_gated_in_portions(ops, H, D, V):

@@ -106,20 +106,6 @@ def _plain_matrix_state(mode, q, k, v, gates, decay, H, G, D, V):
     return o.reshape(n, H * V), S_all
 
 
-@pytest.fixture
-def general_state_kernel():
-    """The decay form on the general kernel (by default it takes the one for forms without feedback)."""
-    from sglang_c_b200.csrc import ops
-    ops.set_kernel_choice(state_without_feedback=False)
-    yield
-    ops.set_kernel_choice(state_without_feedback=True)
-
-
-@pytest.mark.parametrize("H,G,D,V", [(4, 2, 16, 24), (2, 1, 200, 33)])
-def test_decay_form_on_the_general_kernel(general_state_kernel, H, G, D, V):
-    test_matrix_state_recurrences_in_portions("decay", H, G, D, V)
-
-
 @pytest.mark.parametrize("mode", ["delta", "decay"])
 @pytest.mark.parametrize("H,G,D,V", [(4, 2, 16, 24), (2, 2, 64, 80), (3, 1, 7, 5), (2, 1, 200, 33), (1, 1, 128, 1)])
 def test_matrix_state_recurrences_in_portions(mode, H, G, D, V):
