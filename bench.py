@@ -787,8 +787,8 @@ def buborax_config(base, n_layer):
              {"type": "attention", "mixer": {"heads": H, "kv_heads": max(1, H // 4), "dim": 64, "vdim": 64, "scale": 0.125,
                                              "mask": {"size": 256}}, "mlp": mlp}]
     n = max(6, n_layer - 3)
-    return {"architecture": "Buborax", "vocab": base["vocab_size"], "width": E, "residual_mult": 0.5,
-            "norm": {"eps": 1e-5, "groups": 4}, "loop": {"start": 3, "stop": 6, "times": 2},
+    return {"architecture": "Buborax", "vocab": base["vocab_size"], "width": E, "residual_mult": 0.6,
+            "norm": {"eps": 1e-6, "groups": 8}, "loop": {"start": 3, "stop": 6, "times": 2},
             "layers": [kinds[i % 3] for i in range(n)], "max_positions": base["n_positions"]}
 
 

@@ -34,14 +34,14 @@ def _lat(heads, dim, rot_dim, vdim, kv_rank, scale, window, rot_dims, base, ff=N
 # without a window and one without feed-forward; a rotation of part of the turned entries; a
 # multiplier that is no power of two
 BUB_A = {"architecture": "Buborax", "vocab": 300, "width": 64, "residual_mult": 0.7, "norm": {"eps": 1e-6, "groups": 2},
-         "loop": {"start": 1, "stop": 3, "times": 3},
+         "loop": {"start": 1, "stop": 3, "times": 4},
          "layers": [_lat(3, 16, 8, 24, 40, 0.2, 21, 6, 10000.0, 96), _rec(4, 16, 24, 80), _att(4, 2, 16, 0.25, 37, None),
                     _att(2, 1, 32, 0.18, None, 72), _rec(1, 40, 8, None), _lat(2, 24, 16, 16, 48, 0.15, None, 16, 500.0, 64)]}
 # B: sizes the tensor-core products and the tensor-core prompt attention take (latent row of 128 and
 # of 64); no repeated run; one norm group; multiplier one; windows of several pages
 BUB_B = {"architecture": "Buborax", "vocab": 257, "width": 128, "residual_mult": 1.0, "norm": {"eps": 1e-5, "groups": 1},
          "layers": [_att(2, 2, 64, 0.125, 160, 256), _lat(4, 32, 16, 32, 112, 0.125, 150, 16, 20000.0, 144),
-                    _rec(2, 64, 64, 128), _lat(2, 64, 16, 64, 48, 0.1, 70, 16, 10000.0, None), _rec(2, 128, 32, 136)]}
+                    _rec(2, 64, 64, 128), _lat(2, 64, 16, 64, 48, 0.1, 70, 16, 10000.0, None), _rec(2, 128, 32, 120)]}
 # C: sizes that no vector load and no tensor-core tile fits; every layer repeated; one head; a window
 # of one page and a window of three tokens; five norm groups
 BUB_C = {"architecture": "Buborax", "vocab": 101, "width": 50, "residual_mult": 1.3, "norm": {"eps": 1e-5, "groups": 5},

@@ -85,7 +85,7 @@ def test_config_errors_name_the_key():
 
 
 def test_every_pass_keeps_its_own_cache_and_windows_release_pages():
-    """A layer that runs in three passes has three caches (or states); equal needs share a group, so a
+    """A layer that runs in four passes has four caches (or states); equal needs share a group, so a
     page id is valid in all of them; pages behind a window return to the pool."""
     from sglang_c_b200.cache import CacheManager
     from sglang_c_b200.engine.model import Model
@@ -97,13 +97,13 @@ def test_every_pass_keeps_its_own_cache_and_windows_release_pages():
     arch, cfg = _cfg("A")
     model = Model(arch.build_plan(cfg), _Rt())
     needs, cache_of = model.cache_needs()
-    assert len(needs) == 10 and all(n is not None for n in needs)
+    assert len(needs) == 12 and all(n is not None for n in needs)
     cm = CacheManager(needs, cache_of, page_size=16, n_pages=12, max_requests=2)
-    loop_rec = [cm.binding(i) for i in (1, 3, 5)]
-    loop_att = [cm.binding(i) for i in (2, 4, 6)]
+    loop_rec = [cm.binding(i) for i in (1, 3, 5, 7)]
+    loop_att = [cm.binding(i) for i in (2, 4, 6, 8)]
     assert len({b.group for b in loop_rec}) == 1 and len({b.group for b in loop_att}) == 1
     g = cm.groups[loop_att[0].group]
-    assert len(g.calls) == 3 and g.need.window == 37 and g.need.shared and g.need.n_kv_heads == 2
+    assert len(g.calls) == 4 and g.need.window == 37 and g.need.shared and g.need.n_kv_heads == 2
     assert cm.groups[loop_rec[0].group].need.state_shape == (4, 16, 24)
     lat = cm.groups[cm.binding(0).group].need
     assert lat.shared and lat.n_kv_heads == 1 and lat.head_dim == 40 + 8 and lat.window == 21
@@ -113,8 +113,8 @@ def test_every_pass_keeps_its_own_cache_and_windows_release_pages():
     assert cm.extend("a", 100)              # a query at 60 sees 24..60: the first page is gone
     assert [p >= 0 for p in cm.block_table(gi, "a")] == [False, True, True, True, True, True, True]
     assert [p >= 0 for p in cm.block_table(cm.binding(0).group, "a")][:2] == [False, False]
-    none = cm.groups[cm.binding(7).group]
-    assert none.need.window is None and all(p >= 0 for p in cm.block_table(cm.binding(7).group, "a"))
+    none = cm.groups[cm.binding(9).group]
+    assert none.need.window is None and all(p >= 0 for p in cm.block_table(cm.binding(9).group, "a"))
     cm.check()
     cm.free_request("a")
     assert cm.n_free_pages() == 12
