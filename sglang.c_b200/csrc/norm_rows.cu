@@ -285,10 +285,12 @@ SGLC_API int sglc_norm_rows_grouped(const void* src, long long src_stride, int s
   if (add && dst_dtype != SGLC_F32) return SGLC_ERR_ARGUMENT;
   const size_t smem = (size_t)E * sizeof(float);
   if (smem > 200 * 1024) return SGLC_ERR_UNSUPPORTED;
-  const int threads = E >= 2048 ? 512 : (E >= 512 ? 256 : (E >= 128 ? 128 : (E >= 64 ? 64 : 32)));
   const bool vec = src_dtype == SGLC_F32 && E % 4 == 0 && src_stride % 4 == 0 && dst_stride % 4 == 0 && al16(src) &&
                    al16(gain) && al16(bias) &&
                    (reinterpret_cast<uintptr_t>(dst) & (dst_dtype == SGLC_F32 ? 15 : 7)) == 0;
+  // (a narrow part read four floats a thread fills no second warp: one warp then, whose sums are the
+  // same bits, since the second warp only added zeros)
+  const int threads = E >= 2048 ? 512 : (E >= 512 ? 256 : (E >= 128 ? 128 : (E >= 64 && !vec ? 64 : 32)));
 #define LAUNCH(TI, TO, ADD) \
   do {                      \
     if (vec) LAUNCH_V(float, TO, ADD, true); \

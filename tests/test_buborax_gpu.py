@@ -434,7 +434,8 @@ def test_greedy_generation_through_the_scheduler(dirs, name, dtype):
     got = generate(s, prompts, SamplingParams(temperature=0.0), max_new=10)
     for p, g in zip(prompts, got):
         assert len(g) == 10
-        check_greedy(d, p, g, 1e-4 if dtype == "float32" else 5e-2)
+        # (bfloat16: a token whose logit lies within that precision's bound of the best one may win)
+        check_greedy(d, p, g, 1e-4 if dtype == "float32" else TOL["bfloat16"])
     st = s.get_stats()
     assert st.n_finished == len(prompts) and st.pool_free == st.pool_pages
 
