@@ -13,7 +13,7 @@ enum { SGLC_F32 = 0, SGLC_BF16 = 1 };
 // epilogue activations.  The low byte of an `act` argument is the kind; an activation with numbers
 // of its own (xIELU) carries, in the next byte, the slot of this library's parameter table that
 // holds them (sglc_set_act_params fills a slot, once, when a model is loaded).
-enum { SGLC_ACT_NONE = 0, SGLC_ACT_GELU_TANH = 1, SGLC_ACT_GELU_ERF = 2, SGLC_ACT_XIELU = 3 };
+enum { SGLC_ACT_NONE = 0, SGLC_ACT_GELU_TANH = 1, SGLC_ACT_GELU_ERF = 2, SGLC_ACT_XIELU = 3, SGLC_ACT_RELU2 = 4 };
 #define SGLC_ACT_SLOTS 256
 __constant__ float2 c_sglc_act_params[SGLC_ACT_SLOTS];
 
@@ -126,6 +126,10 @@ __device__ __forceinline__ float apply_act(float u, int act) {
     const float2 p = c_sglc_act_params[(act >> 8) & 0xff];
     return xielu_f32(u, p.x, p.y);
   }
+  if (act == SGLC_ACT_RELU2) {                 // the square of relu
+    const float r = fmaxf(u, 0.0f);
+    return r * r;
+  }
   return u;
 }
 
@@ -152,19 +156,26 @@ __device__ __forceinline__ float act_tc(float u, int act) {
   return u;
 }
 // The tensor-core products exist twice: XI = false with the epilogue above, as it always was, and
-// XI = true for xIELU alone.  (One epilogue that chose among all kinds at run time made every
+// XI = true for the activations that came later (xIELU, the squared relu).  (One epilogue that chose among all kinds at run time made every
 // product of a decode step 0.35 us slower, whatever its activation: the unrolled epilogue loops
 // were laid out once per kind.)
 template <bool XI>
 __device__ __forceinline__ float act_tc_k(float u, int act) {
   if constexpr (XI) {
+    if ((act & 0xff) == SGLC_ACT_RELU2) {
+      const float r = fmaxf(u, 0.0f);
+      return r * r;
+    }
     const float2 p = c_sglc_act_params[(act >> 8) & 0xff];
     return xielu_fast(u, p.x, p.y);
   } else {
     return act_tc(u, act);
   }
 }
-__host__ __device__ __forceinline__ bool act_is_xielu(int act) { return (act & 0xff) == SGLC_ACT_XIELU; }
+// (whether an activation belongs to the second instantiation)
+__host__ __device__ __forceinline__ bool act_is_xielu(int act) {
+  return (act & 0xff) == SGLC_ACT_XIELU || (act & 0xff) == SGLC_ACT_RELU2;
+}
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -98,14 +98,15 @@ SGLC_API int sglc_xielu(const void* src, long long src_stride, int src_dtype, vo
 // Gated activation of a feed-forward whose gate and up projections are one product:
 //   dst[r][j] = silu(src[r][j]) * src[r][F + j] * (w ? w[r][j / per] : 1),   j < F
 // src holds the F gate columns, then the F up columns.  With `w` (float [rows][F / per]) a block of
-// `per` columns is one expert of a mixture and takes the token's weight for it (zero: not chosen).
+// `per` columns is one expert of a mixture and takes the token's weight for it (zero: not chosen);
+// columns from `n_weighted` on (an expert that every token uses, laid behind the routed ones) take 1.
 // `act` chooses the gate's function (silu, or the tanh form of GELU); `mult` is one more factor of
 // every result (a layer's residual multiplier, taken in 32-bit ahead of the rounding).
 enum { GA_SILU = 0, GA_GELU_TANH = 1 };
 template <typename TI, typename TO>
 __global__ void gated_act_kernel(const TI* __restrict__ src, long long src_stride, TO* __restrict__ dst,
                                  long long dst_stride, int rows, int F, const float* __restrict__ w,
-                                 long long w_stride, int per, int act, float mult) {
+                                 long long w_stride, int per, int act, float mult, int n_weighted) {
   pdl_launch_dependents();
   pdl_wait();
   const long long total = (long long)rows * F;
@@ -113,7 +114,7 @@ __global__ void gated_act_kernel(const TI* __restrict__ src, long long src_strid
        i += (long long)gridDim.x * blockDim.x) {
     const long long r = i / F;
     const int c = (int)(i % F);
-    const float wt = w ? w[r * w_stride + c / per] : 1.0f;
+    const float wt = (w && c < n_weighted) ? w[r * w_stride + c / per] : 1.0f;
     float out = 0.0f;
     if (wt != 0.0f) {
       const float g = to_f32(src[r * src_stride + c]), u = to_f32(src[r * src_stride + F + c]);
@@ -127,7 +128,8 @@ __global__ void gated_act_kernel(const TI* __restrict__ src, long long src_strid
 // multiples of 8, rows 16-byte aligned
 __global__ void gated_act_vec8_kernel(const __nv_bfloat16* __restrict__ src, long long src_stride,
                                       __nv_bfloat16* __restrict__ dst, long long dst_stride, int rows, int F,
-                                      const float* __restrict__ w, long long w_stride, int per, int act, float mult) {
+                                      const float* __restrict__ w, long long w_stride, int per, int act, float mult,
+                                      int n_weighted) {
   pdl_launch_dependents();
   pdl_wait();
   const int F8 = F / 8;
@@ -136,7 +138,7 @@ __global__ void gated_act_vec8_kernel(const __nv_bfloat16* __restrict__ src, lon
        i += (long long)gridDim.x * blockDim.x) {
     const long long r = i / F8;
     const int c = (int)(i % F8) * 8;
-    const float wt = (w ? w[r * w_stride + c / per] : 1.0f) * mult;
+    const float wt = ((w && c < n_weighted) ? w[r * w_stride + c / per] : 1.0f) * mult;
     uint4 o = make_uint4(0u, 0u, 0u, 0u);
     if (wt != 0.0f) {
       const uint4 g4 = *reinterpret_cast<const uint4*>(src + r * src_stride + c);
@@ -157,30 +159,40 @@ __global__ void gated_act_vec8_kernel(const __nv_bfloat16* __restrict__ src, lon
   }
 }
 
-SGLC_API int sglc_gated_act_ext(const void* src, long long src_stride, int src_dtype, void* dst, long long dst_stride,
-                                int dst_dtype, int rows, int F, const float* w, long long w_stride, int per,
-                                int act, float mult, cudaStream_t stream) {
+// n_weighted: the first so many columns (a multiple of `per`) take weights, the rest take 1
+SGLC_API int sglc_gated_act_part(const void* src, long long src_stride, int src_dtype, void* dst, long long dst_stride,
+                                 int dst_dtype, int rows, int F, const float* w, long long w_stride, int per,
+                                 int act, float mult, int n_weighted, cudaStream_t stream) {
   if (rows <= 0 || F <= 0) return SGLC_OK;
   if (act != GA_SILU && act != GA_GELU_TANH) return SGLC_ERR_ARGUMENT;
-  if (w && (per <= 0 || F % per != 0)) return SGLC_ERR_ARGUMENT;
+  if (w && (per <= 0 || n_weighted < 0 || n_weighted > F || n_weighted % per != 0)) return SGLC_ERR_ARGUMENT;
   const long long total = (long long)rows * F;
   int blocks = (int)((total + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (src_dtype == SGLC_BF16 && dst_dtype == SGLC_BF16 && F % 8 == 0 && src_stride % 8 == 0 && dst_stride % 8 == 0 &&
-      (!w || per % 8 == 0) && (((uintptr_t)src | (uintptr_t)dst) & 15) == 0) {
+      (!w || (per % 8 == 0 && n_weighted % 8 == 0)) && (((uintptr_t)src | (uintptr_t)dst) & 15) == 0) {
     int b8 = (int)((total / 8 + 255) / 256);
     if (b8 > 148 * 16) b8 = 148 * 16;
     return sglc_launch(gated_act_vec8_kernel, dim3(b8), dim3(256), 0, stream, 1, true, (const __nv_bfloat16*)src,
-                       src_stride, (__nv_bfloat16*)dst, dst_stride, rows, F, w, w_stride, per > 0 ? per : 1, act, mult);
+                       src_stride, (__nv_bfloat16*)dst, dst_stride, rows, F, w, w_stride, per > 0 ? per : 1, act, mult,
+                       n_weighted);
   }
 #define LAUNCH(TI, TO)                                                                                  \
   return sglc_launch(gated_act_kernel<TI, TO>, dim3(blocks), dim3(256), 0, stream, 1, true, (const TI*)src, \
-                     src_stride, (TO*)dst, dst_stride, rows, F, w, w_stride, per > 0 ? per : 1, act, mult)
+                     src_stride, (TO*)dst, dst_stride, rows, F, w, w_stride, per > 0 ? per : 1, act, mult, n_weighted)
   if (src_dtype == SGLC_F32 && dst_dtype == SGLC_F32) LAUNCH(float, float);
   if (src_dtype == SGLC_F32 && dst_dtype == SGLC_BF16) LAUNCH(float, __nv_bfloat16);
   if (src_dtype == SGLC_BF16 && dst_dtype == SGLC_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
 #undef LAUNCH
   return SGLC_ERR_ARGUMENT;
+}
+
+SGLC_API int sglc_gated_act_ext(const void* src, long long src_stride, int src_dtype, void* dst, long long dst_stride,
+                                int dst_dtype, int rows, int F, const float* w, long long w_stride, int per,
+                                int act, float mult, cudaStream_t stream) {
+  if (w && (per <= 0 || F % per != 0)) return SGLC_ERR_ARGUMENT;
+  return sglc_gated_act_part(src, src_stride, src_dtype, dst, dst_stride, dst_dtype, rows, F, w, w_stride, per, act,
+                             mult, F, stream);
 }
 
 SGLC_API int sglc_gated_act(const void* src, long long src_stride, int src_dtype, void* dst, long long dst_stride,
@@ -217,5 +229,49 @@ SGLC_API int sglc_cast_rows(const float* src, long long src_stride, void* dst, l
   if (dst_dtype == SGLC_BF16)
     return sglc_launch(cast_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, 1, true, src, src_stride,
                        (__nv_bfloat16*)dst, dst_stride, rows, cols);
+  return SGLC_ERR_ARGUMENT;
+}
+
+// A gate times a row of a token table: dst[t][j] = act(z[t][j]) * table[tokens[t]][first + j], j < cols
+// (act: the tanh form of GELU).  z: 32-bit rows; the table float or bfloat16 with rows of `table_cols`;
+// a token id outside the table raises the error word and gives zeros.
+template <typename TW, typename TO>
+__global__ void gated_gather_kernel(const float* __restrict__ z, long long z_stride, const int* __restrict__ tokens,
+                                    const TW* __restrict__ table, long long table_cols, int n_table_rows, int first,
+                                    TO* __restrict__ dst, long long dst_stride, int rows, int cols,
+                                    int* __restrict__ err) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long total = (long long)rows * cols;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / cols;
+    const int c = (int)(i % cols);
+    const int tok = tokens[r];
+    float out = 0.0f;
+    if (tok >= 0 && tok < n_table_rows)
+      out = gelu_tanh_f32(z[r * z_stride + c]) * to_f32(table[(size_t)tok * table_cols + first + c]);
+    else if (err)
+      atomicExch(err, 1);
+    dst[r * dst_stride + c] = from_f32<TO>(out);
+  }
+}
+
+SGLC_API int sglc_gated_gather(const float* z, long long z_stride, const int* tokens, const void* table,
+                               long long table_cols, int n_table_rows, int first, int table_dtype, void* dst,
+                               long long dst_stride, int dst_dtype, int rows, int cols, int* err, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return SGLC_OK;
+  if (first < 0 || first + cols > table_cols || n_table_rows <= 0) return SGLC_ERR_ARGUMENT;
+  const long long total = (long long)rows * cols;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+#define LAUNCH(TW, TO)                                                                                        \
+  return sglc_launch(gated_gather_kernel<TW, TO>, dim3(blocks), dim3(256), 0, stream, 1, true, z, z_stride, tokens, \
+                     (const TW*)table, table_cols, n_table_rows, first, (TO*)dst, dst_stride, rows, cols, err)
+  if (table_dtype == SGLC_F32 && dst_dtype == SGLC_F32) LAUNCH(float, float);
+  if (table_dtype == SGLC_BF16 && dst_dtype == SGLC_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  if (table_dtype == SGLC_BF16 && dst_dtype == SGLC_F32) LAUNCH(__nv_bfloat16, float);
+  if (table_dtype == SGLC_F32 && dst_dtype == SGLC_BF16) LAUNCH(float, __nv_bfloat16);
+#undef LAUNCH
   return SGLC_ERR_ARGUMENT;
 }

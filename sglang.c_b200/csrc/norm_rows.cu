@@ -16,7 +16,7 @@
 
 SGLC_DEFINE_ERROR_STRING()
 
-enum { NORM_LAYER = 0, NORM_RMS = 1 };
+enum { NORM_LAYER = 0, NORM_RMS = 1, NORM_COPY = 2 };   // NORM_COPY: the tail's second stage only, no norm
 
 // Four floats at a time (VEC: a 32-bit source whose rows, gains and destination can be read and
 // written 16 bytes at a time).  A thread's order of additions differs between the two forms; which
@@ -125,7 +125,8 @@ __global__ void norm_rows_kernel(const TI* __restrict__ src, long long src_strid
 // The tail of a sublayer in one launch, a block a row:
 //   x += norm_post(y) * g_post                                   (x: the 32-bit stream)
 //   [mix]   hist[n_terms-1] = x;  x = sum_j w[j] * hist[j]        (a depth-weighted average, j ascending)
-//   [next]  h = norm_next(x) * g_next                            (the norm ahead of the next sublayer)
+//   [next]  h = norm_next(x) * g_next                            (the norm ahead of the next sublayer;
+//                                                                  form NORM_COPY: h = x in h's precision)
 // The same arithmetic in the same order as the three kernels it stands for, so the bits are theirs.
 template <typename TO, bool VEC>
 __global__ void norm_add_tail_kernel(const float* __restrict__ y, long long y_stride,
@@ -211,6 +212,15 @@ __global__ void norm_add_tail_kernel(const float* __restrict__ y, long long y_st
     }
   }
   if (!h) return;
+  if (form_next == NORM_COPY) {
+    __syncthreads();
+    TO* hc = h + (size_t)r * h_stride;
+    for (int i = threadIdx.x; i < n_it; i += blockDim.x) {
+      if constexpr (VEC) store4<TO>(hc + 4 * i, reinterpret_cast<const float4*>(srow)[i]);
+      else hc[i] = from_f32<TO>(srow[i]);
+    }
+    return;
+  }
   mean = 0.0f;
   if (form_next == NORM_LAYER) mean = block_sum(s, red) / (float)E;
   else __syncthreads();

@@ -9,7 +9,7 @@ import torch
 from . import build
 
 F32, BF16 = 0, 1
-ACT = {None: 0, "none": 0, "gelu_tanh": 1, "gelu_erf": 2, "xielu": 3}
+ACT = {None: 0, "none": 0, "gelu_tanh": 1, "gelu_erf": 2, "xielu": 3, "relu2": 4}
 ACT_SLOTS = 256              # parameter slots per kernel library (common.cuh: SGLC_ACT_SLOTS)
 _act_slots = []              # slot -> (a, b), as registered
 _act_synced = {}             # library name -> slots already written into it
@@ -677,7 +677,7 @@ def sample(logits, params, hist_tok, hist_cnt, out_tok, out_logprob=None):
 
 
 # ---------------------------------------------------------------------------
-NORM_FORMS = {"layer": 0, "rms": 1}
+NORM_FORMS = {"layer": 0, "rms": 1, "copy": 2}      # "copy": norm_add_tail's `then` stage only
 
 
 def norm_rows(src, gain, bias, eps, dst, form="layer", add=False, dst_rows=None, src_rows=None, groups=1):
@@ -724,7 +724,8 @@ def norm_add_tail(y, gain, eps, x, form="layer", mix=None, then=None):
     """x += norm(y) * gain (x: float32 [T,E], the residual stream; y float32 [T,E]); then, in the same
     launch, mix = (hist, n_terms, weights): hist[n_terms-1] = x, x = sum_j weights[j] * hist[j]
     (as depth_mix), and then = (gain, eps, form, out): out = norm(x) * gain (the norm ahead of the
-    next sublayer).  The bits are those of the separate kernels."""
+    next sublayer; form "copy" with gain None: out = x in out's precision, for a sublayer that reads
+    the stream itself).  The bits are those of the separate kernels."""
     hist, n_terms, weights = mix if mix is not None else (None, 0, None)
     g2, eps2, form2, out = then if then is not None else (None, 0.0, "layer", None)
     _need_cuda(y, gain, x, hist, weights, g2, out)
@@ -737,6 +738,8 @@ def norm_add_tail(y, gain, eps, x, form="layer", mix=None, then=None):
         raise KernelError("norm_add_tail: hist is float32 [>= n_terms, T, E] for this step's T")
     if out is not None and (tuple(out.shape) != (n, E) or out.stride(1) != 1):
         raise KernelError("norm_add_tail: the next norm's output is [T,E]")
+    if form == "copy" or (form2 == "copy") != (then is not None and g2 is None):
+        raise KernelError("norm_add_tail: \"copy\" is the second stage's form, and goes without a gain")
     lib = build.load("norm_rows")
     code = lib.sglc_norm_add_tail(_ptr(y), ctypes.c_longlong(y.stride(0)), _ptr(gain), ctypes.c_float(eps),
                                   NORM_FORMS[form], _ptr(x), _ptr(hist),
@@ -881,19 +884,24 @@ MATRIX_STATE_MAX_DIM = 256
 
 
 def matrix_state(mode, q, k, v, out, state, q_start, state_slots, n_requests, n_heads, n_qk_heads, dim, v_dim,
-                 gates=None, head_decay=None, silu_in=False, lower=None):
+                 gates=None, head_decay=None, silu_in=False, lower=None, row_z=None, tau=1.0, q_scale=1.0,
+                 ones_col=False):
     """A recurrence with a matrix state per head over the step's tokens (see matrix_state.cu).
     mode "decay": S <- d_h S + k v^T (head_decay float32 [H]); mode "delta": the gated delta rule
     (gates float32 [T, 2H]: beta, then decay); mode "row_gate": S <- diag(f) S + (1 - f) v^T with
     f = lower + (1 - lower) sigmoid(k) per head and row (k holds the gates' pre-activations, lower
-    float32 [H*dim]; silu_in then acts on q only).  o = S^T q after the token's write.  q, k: float32
+    float32 [H*dim]; silu_in then acts on q only); mode "row_decay": S <- diag(a) S + k v^T with
+    a = sigmoid(row_z)^(1/tau) per head and row (row_z float32 [T, n_qk_heads*dim]); mode "gated":
+    S <- g S + b k v^T (gates float32 [T, 2H]: b, then g); with ones_col the state (and out) have
+    v_dim columns a head of which the last takes the value 1 for every token, and v has heads of
+    v_dim - 1.  q_scale multiplies q.  o = S^T q after the token's write.  q, k: float32
     [T, n_qk_heads*dim]; v: float32 [T, n_heads*v_dim]; out float32 [T, n_heads*v_dim]; state float32
     [n_slots, n_heads, dim, v_dim], read and written in place for the requests' slots."""
     _need_cuda(q, k, v, out, state, q_start, state_slots, gates, head_decay, lower)
     T = out.shape[0]
     _f32_rows(q, "matrix_state: q", n_qk_heads * dim)
     _f32_rows(k, "matrix_state: k", n_qk_heads * dim)
-    _f32_rows(v, "matrix_state: v", n_heads * v_dim)
+    _f32_rows(v, "matrix_state: v", n_heads * (v_dim - 1 if ones_col else v_dim))
     _f32_rows(out, "matrix_state: out", n_heads * v_dim)
     if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (n_heads, dim, v_dim):
         raise KernelError(f"matrix_state: the state is float32 [n_slots, {n_heads}, {dim}, {v_dim}]")
@@ -901,49 +909,68 @@ def matrix_state(mode, q, k, v, out, state, q_start, state_slots, n_requests, n_
         raise KernelError(f"matrix_state: key size {dim} is beyond the kernel's {MATRIX_STATE_MAX_DIM}")
     _i32(q_start, "q_start")
     _i32(state_slots, "state_slots")
-    m = {"decay": 0, "delta": 1, "row_gate": 2}[mode]
+    m = {"decay": 0, "delta": 1, "row_gate": 2, "row_decay": 3, "gated": 4}[mode]
+    if ones_col and m != 4:
+        raise KernelError("matrix_state: the column of ones goes with the gated form")
+    if m == 3:
+        if row_z is None:
+            raise KernelError("matrix_state: the row-decay form takes the decays' pre-activations")
+        _need_cuda(row_z)
+        _f32_rows(row_z, "matrix_state: row_z", n_qk_heads * dim)
     if m == 2 and (lower is None or lower.dtype != torch.float32 or lower.numel() != n_heads * dim
                    or not lower.is_contiguous() or n_qk_heads != n_heads):
         raise KernelError("matrix_state: the row-gated form takes one float32 lower bound per head and row, "
                           "and as many gate heads as value heads")
     if m == 0 and (head_decay is None or head_decay.dtype != torch.float32 or head_decay.numel() != n_heads):
         raise KernelError("matrix_state: the decay form takes one float32 decay per head")
-    if m == 1:
+    if m in (1, 4):
         if gates is None:
-            raise KernelError("matrix_state: the delta rule takes its gates")
+            raise KernelError("matrix_state: the delta rule and the gated form take their gates")
         _f32_rows(gates, "matrix_state: gates", 2 * n_heads)
     lib = build.load("matrix_state")
-    code = lib.sglc_matrix_state_ext(m, _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(k), ctypes.c_longlong(k.stride(0)),
+    code = lib.sglc_matrix_state_gen(m, _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(k), ctypes.c_longlong(k.stride(0)),
                                  _ptr(v), ctypes.c_longlong(v.stride(0)), _ptr(gates),
                                  ctypes.c_longlong(gates.stride(0) if gates is not None else 0), _ptr(head_decay),
-                                 _ptr(lower), _ptr(out), ctypes.c_longlong(out.stride(0)), _ptr(state), state.shape[0],
+                                 _ptr(lower), _ptr(row_z), ctypes.c_longlong(row_z.stride(0) if row_z is not None else 0),
+                                 ctypes.c_float(1.0 / float(tau)), ctypes.c_float(q_scale), 1 if ones_col else 0,
+                                 _ptr(out), ctypes.c_longlong(out.stride(0)), _ptr(state), state.shape[0],
                                  _ptr(q_start), _ptr(state_slots), int(n_requests), int(n_heads), int(n_qk_heads),
                                  int(dim), int(v_dim), 1 if silu_in else 0, _ptr(tc_error_flag(q.device)), _stream())
     _check(lib, code, f"matrix_state ({mode}, {dim} x {v_dim})")
 
 
-def gated_norm(o, gate, gain, y, groups, width, eps, act):
+def gated_norm(o, gate, gain, y, groups, width, eps, act, o_pitch=None, m_run=None):
     """y = o / sqrt(mean(o^2) + eps) * gain * act(gate) per row of `width` (a token has `groups`
-    rows side by side; gain float32 [width] serves them all); act "silu" or "sigmoid", or "none"
-    with gate None: the norm alone.  o, gate: float32 [T, groups*width]; y: float32 or bfloat16."""
-    _need_cuda(o, gate, gain, y)
+    rows side by side; gain float32 [width] serves them all, or [groups*width] every row its own);
+    act "silu" or "sigmoid", or "none" with gate None: the norm alone.  o, gate: float32
+    [T, groups*width]; y: float32 or bfloat16.  o_pitch: the rows of a token lie so many columns
+    apart in o (default width).  m_run (float32 [T, groups], with o_pitch > width): ahead of the
+    norm a row is divided by max(|o[width]|, exp(-m_run)) + 1e-6, o[width] being the column behind it."""
+    _need_cuda(o, gate, gain, y, m_run)
     T = y.shape[0]
-    _f32_rows(o, "gated_norm: o", groups * width)
+    o_pitch = width if o_pitch is None else int(o_pitch)
+    _f32_rows(o, "gated_norm: o", groups * o_pitch)
+    if m_run is not None:
+        _f32_rows(m_run, "gated_norm: m_run", groups)
+        if o_pitch < width + 1 or m_run.shape[0] < T:
+            raise KernelError("gated_norm: the divisor's column lies behind the row")
     if (act == "none") != (gate is None):
         raise KernelError("gated_norm: a gate goes with silu or sigmoid, none with \"none\"")
     if gate is not None:
         _f32_rows(gate, "gated_norm: gate", groups * width)
-    if gain.dtype != torch.float32 or gain.numel() != width or not gain.is_contiguous():
-        raise KernelError("gated_norm: the gain is a float32 vector of the row width")
+    if gain.dtype != torch.float32 or gain.numel() not in (width, groups * width) or not gain.is_contiguous():
+        raise KernelError("gated_norm: the gain is a float32 vector of the row width (or of all rows of a token)")
     if tuple(y.shape) != (T, groups * width) or y.stride(1) != 1 or o.shape[0] < T \
             or (gate is not None and gate.shape[0] < T):
         raise KernelError("gated_norm: y is [T, groups*width]")
     lib = build.load("gated_norm")
-    code = lib.sglc_gated_norm(_ptr(o), ctypes.c_longlong(o.stride(0)), _ptr(gate),
-                               ctypes.c_longlong(gate.stride(0) if gate is not None else 0),
-                               _ptr(gain), _ptr(y), ctypes.c_longlong(y.stride(0)), _dt(y, "gated_norm output"), T,
-                               int(groups), int(width), ctypes.c_float(eps), {"silu": 0, "sigmoid": 1, "none": 2}[act],
-                               _stream())
+    code = lib.sglc_gated_norm_ext(_ptr(o), ctypes.c_longlong(o.stride(0)), _ptr(gate),
+                                   ctypes.c_longlong(gate.stride(0) if gate is not None else 0),
+                                   _ptr(gain), _ptr(y), ctypes.c_longlong(y.stride(0)), _dt(y, "gated_norm output"), T,
+                                   int(groups), int(width), ctypes.c_float(eps),
+                                   {"silu": 0, "sigmoid": 1, "none": 2}[act], o_pitch,
+                                   1 if (gain.numel() == groups * width and groups > 1) else 0, _ptr(m_run),
+                                   ctypes.c_longlong(m_run.stride(0) if m_run is not None else 0), _stream())
     _check(lib, code, f"gated_norm (width {width})")
 
 
@@ -972,6 +999,91 @@ def rotary_kv(x, positions, freq, mult, dims, norm_eps, q_out, cache, slots, n_h
                               int(n_kv_heads), int(dim), int(v_dim), int(page_size), n_pages, _dt(q_out, "queries"),
                               _ptr(tc_error_flag(x.device)), _stream())
     _check(lib, code, f"rotary_kv (head {dim})")
+
+
+QK_NORMS = {None: 0, False: 0, "none": 0, True: 1, "unit": 1, "head_gain": 2, "row_gain": 3}
+
+
+def qk_prep(x, positions, freq, mult, dims, pairing, norm, eps, gain_q, gain_k, q_out, cache, slots, n_heads,
+            n_kv_heads, dim, v_dim, page_size, v_mult=1.0):
+    """The general input stage of a softmax attention (rotary.cu: qk_prep_kernel).  x: float32 rows
+    [T, H*dim | G*dim | G*v_dim], or [T, H*dim] alone with n_kv_heads = 0 (a layer that reads keys and
+    values another layer cached: cache and slots are then None).  norm: None; "unit" (after the
+    turn, no gain); "head_gain" (before the turn, per head, gains float32 [dim] shared by the heads);
+    "row_gain" (before the turn, one root mean square over all query heads and one over all key
+    heads, gains float32 [H*dim] and [G*dim]).  pairing "halves" or "neighbours".  Queries go to q_out
+    [T, H*dim]; keys and values (times v_mult) into the cache's pages at slots."""
+    _need_cuda(x, positions, freq, q_out, cache, slots, gain_q, gain_k)
+    T = q_out.shape[0]
+    G = int(n_kv_heads)
+    _f32_rows(x, "qk_prep: x", n_heads * dim + G * (dim + v_dim))
+    _i32(positions, "positions")
+    mode = QK_NORMS[norm]
+    if dims and (freq is None or freq.dtype != torch.float64 or freq.numel() != dims // 2 or not freq.is_contiguous()):
+        raise KernelError("qk_prep: one float64 frequency per turned pair")
+    if q_out.shape[1] != n_heads * dim or q_out.stride(1) != 1:
+        raise KernelError("qk_prep: queries [T, H*dim]")
+    n_pages = 0
+    if G:
+        _i32(slots, "slots")
+        n_pages = cache.shape[0]
+        if q_out.dtype != cache.dtype or not cache.is_contiguous() \
+                or cache.numel() != n_pages * G * page_size * (dim + v_dim):
+            raise KernelError(f"qk_prep: cache {tuple(cache.shape)} does not fit {G} heads of {dim}+{v_dim}, or its "
+                              "dtype is not the queries'")
+    want = {2: (dim, dim), 3: (n_heads * dim, G * dim)}.get(mode)
+    if want is not None:
+        for g, n, nm in ((gain_q, want[0], "queries"), (gain_k, want[1], "keys")):
+            if n and (g is None or g.dtype != torch.float32 or g.numel() != n or not g.is_contiguous()):
+                raise KernelError(f"qk_prep: the gain of the {nm} is a float32 vector of {n}")
+    lib = build.load("rotary")
+    code = lib.sglc_qk_prep(_ptr(x), ctypes.c_longlong(x.stride(0)), _ptr(positions), _ptr(freq if dims else None),
+                            ctypes.c_float(mult), int(dims), ROTARY_PAIRINGS[pairing], mode, ctypes.c_float(eps or 0.0),
+                            _ptr(gain_q), _ptr(gain_k if G else None), ctypes.c_float(v_mult), _ptr(q_out),
+                            ctypes.c_longlong(q_out.stride(0)), _ptr(cache if G else None), _ptr(slots if G else None),
+                            T, int(n_heads), G, int(dim), int(v_dim), int(page_size), n_pages, _dt(q_out, "queries"),
+                            _ptr(tc_error_flag(x.device)), _stream())
+    _check(lib, code, f"qk_prep (head {dim})")
+
+
+def stabilized_gates(xi, xf, cap, gates, m_out, m_state, q_start, state_slots, n_requests, n_heads):
+    """Exponential gates with a running maximum per (request, head) (matrix_state.cu:
+    stabilized_gates_kernel).  xi, xf: float32 [T, n_heads] views (the input and forget gates'
+    pre-activations, biases included); gates: float32 [T, 2*n_heads] (input weight, then decay);
+    m_out: float32 [T, n_heads]; m_state: float32 [n_slots, n_heads], read and written in place."""
+    _need_cuda(xi, xf, gates, m_out, m_state, q_start, state_slots)
+    _f32_rows(xi, "stabilized_gates: xi", n_heads)
+    _f32_rows(xf, "stabilized_gates: xf", n_heads)
+    _f32_rows(gates, "stabilized_gates: gates", 2 * n_heads)
+    _f32_rows(m_out, "stabilized_gates: m_out", n_heads)
+    if m_state.dtype != torch.float32 or not m_state.is_contiguous() or tuple(m_state.shape[1:]) != (n_heads,):
+        raise KernelError(f"stabilized_gates: the running maxima are float32 [n_slots, {n_heads}]")
+    _i32(q_start, "q_start")
+    _i32(state_slots, "state_slots")
+    lib = build.load("matrix_state")
+    code = lib.sglc_stabilized_gates(_ptr(xi), ctypes.c_longlong(xi.stride(0)), _ptr(xf), ctypes.c_longlong(xf.stride(0)),
+                                     ctypes.c_float(cap), _ptr(gates), ctypes.c_longlong(gates.stride(0)), _ptr(m_out),
+                                     ctypes.c_longlong(m_out.stride(0)), _ptr(m_state), m_state.shape[0], _ptr(q_start),
+                                     _ptr(state_slots), int(n_requests), int(n_heads), _ptr(tc_error_flag(xi.device)),
+                                     _stream())
+    _check(lib, code, f"stabilized_gates ({n_heads} heads)")
+
+
+def gated_gather(z, tokens, table, first, dst, err_flag=None):
+    """dst[t, j] = gelu_tanh(z[t, j]) * table[tokens[t], first + j] for the columns dst has; z float32
+    rows; table float32 or bfloat16 [rows, cols]."""
+    _need_cuda(z, tokens, table, dst)
+    rows, cols = dst.shape
+    _f32_rows(z, "gated_gather: z")
+    _i32(tokens, "tokens")
+    if z.shape[0] < rows or z.shape[1] < cols or dst.stride(1) != 1 or table.dim() != 2 or not table.is_contiguous():
+        raise KernelError("gated_gather: z float32 [>= rows, >= cols]; dst rows contiguous; a contiguous table")
+    lib = build.load("elementwise")
+    code = lib.sglc_gated_gather(_ptr(z), ctypes.c_longlong(z.stride(0)), _ptr(tokens), _ptr(table),
+                                 ctypes.c_longlong(table.shape[1]), table.shape[0], int(first), _dt(table, "table"),
+                                 _ptr(dst), ctypes.c_longlong(dst.stride(0)), _dt(dst, "gated_gather destination"),
+                                 rows, cols, _ptr(err_flag), _stream())
+    _check(lib, code, "gated_gather")
 
 
 def attention_ext(q, cache, block_table, token_req, positions, out, n_heads, n_kv_heads, dim, v_dim, page_size,
@@ -1005,31 +1117,38 @@ def attention_ext(q, cache, block_table, token_req, positions, out, n_heads, n_k
 GATE_ACTS = {"silu": 0, "gelu_tanh": 1}
 
 
-def gated_act(src, dst, weights=None, per=0, act="silu", mult=1.0):
+def gated_act(src, dst, weights=None, per=0, act="silu", mult=1.0, n_weighted=None):
     """dst[r, j] = act(src[r, j]) * src[r, F + j] (* weights[r, j // per]) * mult; src [rows, 2F] holds
     the gate columns, then the up columns; weights: float32 [rows, F // per] or None; act "silu" or
-    "gelu_tanh"; mult: one more factor of every result, taken in 32-bit."""
+    "gelu_tanh"; mult: one more factor of every result, taken in 32-bit.  n_weighted: only the
+    first so many columns (a multiple of per) take weights, [rows, n_weighted // per]; the rest take 1."""
     _need_cuda(src, dst, weights)
     rows, F = dst.shape
     if src.shape[1] != 2 * F or src.shape[0] < rows or src.stride(1) != 1 or dst.stride(1) != 1:
         raise KernelError("gated_act: src [rows, 2F], dst [rows, F]")
     if weights is not None:
         _f32_rows(weights, "gated_act: weights")
-        if per <= 0 or F % per or weights.shape[1] != F // per or weights.shape[0] < rows:
+        nw = F if n_weighted is None else int(n_weighted)
+        if per <= 0 or nw % per or nw > F or weights.shape[1] != nw // per or weights.shape[0] < rows:
             raise KernelError("gated_act: one weight per row and block of `per` columns")
+    else:
+        nw = F
     lib = build.load("elementwise")
-    code = lib.sglc_gated_act_ext(_ptr(src), ctypes.c_longlong(src.stride(0)), _dt(src, "gated_act source"), _ptr(dst),
-                                  ctypes.c_longlong(dst.stride(0)), _dt(dst, "gated_act destination"), rows, F,
-                                  _ptr(weights), ctypes.c_longlong(weights.stride(0) if weights is not None else 0),
-                                  int(per), GATE_ACTS[act], ctypes.c_float(mult), _stream())
+    code = lib.sglc_gated_act_part(_ptr(src), ctypes.c_longlong(src.stride(0)), _dt(src, "gated_act source"), _ptr(dst),
+                                   ctypes.c_longlong(dst.stride(0)), _dt(dst, "gated_act destination"), rows, F,
+                                   _ptr(weights), ctypes.c_longlong(weights.stride(0) if weights is not None else 0),
+                                   int(per), GATE_ACTS[act], ctypes.c_float(mult), nw, _stream())
     _check(lib, code, "gated_act")
 
 
 ROUTER_MAX_EXPERTS = 256
 
 
-def router(logits, correction, dense, ids, weights, top, n_groups=1, keep=1, renorm=False, weight_scale=1.0):
-    """Sigmoid routing with a choice correction and group limits (see router.cu).  logits: float32
+def router(logits, correction, dense, ids, weights, top, n_groups=1, keep=1, renorm=False, weight_scale=1.0,
+           score="sigmoid", renorm_eps=0.0):
+    """Routing by sigmoid scores (or, score "softmax", a softmax over all experts) with a choice
+    correction and group limits; renorm: the chosen scores divided by their sum + renorm_eps; then
+    times weight_scale (see router.cu).  logits: float32
     [T, E]; correction: float32 [E] or None; dense: float32 [T, E] (weights, zero where not
     chosen); ids int32 [T, top]; weights float32 [T, top]."""
     _need_cuda(logits, correction, dense, ids, weights)
@@ -1042,9 +1161,10 @@ def router(logits, correction, dense, ids, weights, top, n_groups=1, keep=1, ren
     if correction is not None and (correction.dtype != torch.float32 or correction.numel() != E):
         raise KernelError("router: one float32 correction per expert")
     lib = build.load("router")
-    code = lib.sglc_router(_ptr(logits), ctypes.c_longlong(logits.stride(0)), _ptr(correction), _ptr(dense),
-                           ctypes.c_longlong(dense.stride(0)), _ptr(ids), _ptr(weights), T, E, int(top), int(n_groups),
-                           int(keep), 1 if renorm else 0, ctypes.c_float(weight_scale), _stream())
+    code = lib.sglc_router_ext(_ptr(logits), ctypes.c_longlong(logits.stride(0)), _ptr(correction), _ptr(dense),
+                               ctypes.c_longlong(dense.stride(0)), _ptr(ids), _ptr(weights), T, E, int(top),
+                               int(n_groups), int(keep), 1 if renorm else 0, ctypes.c_float(weight_scale),
+                               {"sigmoid": 0, "softmax": 1}[score], ctypes.c_float(renorm_eps), _stream())
     _check(lib, code, f"router ({E} experts, {top} chosen)")
 
 

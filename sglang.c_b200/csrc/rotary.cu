@@ -172,3 +172,138 @@ SGLC_API int sglc_latent_rope(const float* qx, long long qx_stride, const float*
                        (__nv_bfloat16*)q_out, q_stride, (__nv_bfloat16*)rows, slots, n_rows, T, H, R, Rd, err);
   return SGLC_ERR_ARGUMENT;
 }
+
+// The general input stage of a softmax attention, a block a token: 32-bit rows x holding H query
+// heads of D, then (with G > 0: a layer that owns its keys and values) G key heads of D and G value
+// heads of V.  Per head, in this order:
+//   norm (norm_mode)   0: none.  1: after the turn, the head divided by its root mean square, no gain.
+//                      2: before the turn, the head divided by its root mean square times a gain of
+//                         D entries that the heads share (gain_q for queries, gain_k for keys).
+//                      3: before the turn, all query heads of the token divided by ONE root mean
+//                         square over their H*D entries, times a gain of H*D entries (gain_q); the key
+//                         heads likewise over G*D entries (gain_k).
+//   turn               the first `dims` entries by position * freq[i], pairs (i, i + dims/2)
+//                      (pairing 0) or (2i, 2i + 1) (pairing 1); the rest pass.
+// Queries leave as [T][H*D] in the activation precision; keys and values go to their cache page
+// (G x page_size x D keys, then G x page_size x V values) at slots[t]; values are multiplied by
+// v_mult on the way (a mixer whose result is a fixed multiple of the attention's folds it here:
+// the attention is linear in its values).  eps lies inside every root.
+template <typename TA>
+__global__ void __launch_bounds__(ROT_WARPS * 32)
+qk_prep_kernel(const float* __restrict__ x, long long x_stride, const int* __restrict__ positions,
+               const double* __restrict__ freq, float mult, int dims, int pairing, int norm_mode, float eps,
+               const float* __restrict__ gain_q, const float* __restrict__ gain_k, float v_mult,
+               TA* __restrict__ q_out, long long q_stride, TA* __restrict__ cache, const int* __restrict__ slots,
+               int T, int H, int G, int D, int V, int page_size, int n_pages, int* err) {
+  __shared__ float buf[ROT_WARPS][ROT_MAX_DIM];
+  __shared__ float red[2][ROT_WARPS];
+  pdl_launch_dependents();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_wait();
+  const int pos = positions[t];
+  const int slot = G > 0 ? slots[t] : -1;
+  const int page = slot / page_size, off = slot % page_size;
+  const bool page_ok = G > 0 && slot >= 0 && sglc_index_ok(page, n_pages, err);
+  const size_t page_elems = (size_t)G * page_size * (D + V);
+  const float* xr = x + (size_t)t * x_stride;
+  const int half = dims / 2;
+  float inv_all[2] = {1.0f, 1.0f};
+  if (norm_mode == 3) {
+    // one root mean square over all query heads, one over all key heads: every thread sums its
+    // share in a fixed order, so a token's bits do not depend on the rest of the step
+    float sq = 0.0f, sk = 0.0f;
+    for (int i = threadIdx.x; i < H * D; i += ROT_WARPS * 32) sq = fmaf(xr[i], xr[i], sq);
+    for (int i = threadIdx.x; i < G * D; i += ROT_WARPS * 32) sk = fmaf(xr[H * D + i], xr[H * D + i], sk);
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    if (lane == 0) { red[0][warp] = sq; red[1][warp] = sk; }
+    __syncthreads();
+    sq = 0.0f; sk = 0.0f;
+    for (int w = 0; w < ROT_WARPS; w++) { sq += red[0][w]; sk += red[1][w]; }
+    inv_all[0] = 1.0f / sqrtf(sq / (float)(H * D) + eps);
+    if (G > 0) inv_all[1] = 1.0f / sqrtf(sk / (float)(G * D) + eps);
+  }
+  float* b = buf[warp];
+  for (int row = warp; row < H + 2 * G; row += ROT_WARPS) {
+    if (row >= H + G) {                        // a value head: copied (times v_mult)
+      const int g = row - H - G;
+      if (page_ok) {
+        TA* dst = cache + (size_t)page * page_elems + (size_t)G * page_size * D + ((size_t)g * page_size + off) * V;
+        const float* src = xr + (size_t)(H + G) * D + (size_t)g * V;
+        for (int d = lane; d < V; d += 32) dst[d] = from_f32<TA>(src[d] * v_mult);
+      }
+      continue;
+    }
+    const bool is_q = row < H;
+    const float* src = xr + (size_t)row * D;
+    float ss = 0.0f;
+    for (int d = lane; d < D; d += 32) {
+      const float u = src[d];
+      b[d] = u;
+      ss = fmaf(u, u, ss);
+    }
+    if (norm_mode == 2) {
+      ss = warp_sum(ss);
+      const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+      const float* gn = is_q ? gain_q : gain_k;
+      for (int d = lane; d < D; d += 32) b[d] = __fmul_rn(__fmul_rn(b[d], inv), gn[d]);
+    } else if (norm_mode == 3) {
+      const float inv = inv_all[is_q ? 0 : 1];
+      const float* gn = is_q ? gain_q + (size_t)row * D : gain_k + (size_t)(row - H) * D;
+      for (int d = lane; d < D; d += 32) b[d] = __fmul_rn(__fmul_rn(b[d], inv), gn[d]);
+    }
+    __syncwarp();
+    ss = 0.0f;
+    for (int i = lane; i < half; i += 32) {
+      double a = (double)pos * freq[i];
+      a -= floor(a * 0.15915494309189535) * 6.283185307179586;
+      float sn, cs;
+      sincosf((float)a, &sn, &cs);
+      sn *= mult; cs *= mult;
+      const int iu = pairing ? 2 * i : i, iv = pairing ? 2 * i + 1 : i + half;
+      const float u = b[iu], v = b[iv];
+      const float ru = u * cs - v * sn, rv = v * cs + u * sn;
+      b[iu] = ru; b[iv] = rv;
+      ss = fmaf(ru, ru, fmaf(rv, rv, ss));
+    }
+    float f = 1.0f;
+    if (norm_mode == 1) {
+      for (int d = 2 * half + lane; d < D; d += 32) ss = fmaf(b[d], b[d], ss);
+      ss = warp_sum(ss);
+      f = 1.0f / sqrtf(ss / (float)D + eps);
+    }
+    __syncwarp();
+    TA* dst = nullptr;
+    if (is_q) dst = q_out + (size_t)t * q_stride + (size_t)row * D;
+    else if (page_ok) dst = cache + (size_t)page * page_elems + ((size_t)(row - H) * page_size + off) * D;
+    if (dst)
+      for (int d = lane; d < D; d += 32) dst[d] = from_f32<TA>(b[d] * f);
+    __syncwarp();
+  }
+}
+
+// x: float [T][H*D (+ G*D + G*V)]; G = 0: queries only (cache and slots unused); gain_q, gain_k:
+// float, [D] each (norm_mode 2) or [H*D] and [G*D] (norm_mode 3), else unused.
+SGLC_API int sglc_qk_prep(const float* x, long long x_stride, const int* positions, const double* freq, float mult,
+                          int dims, int pairing, int norm_mode, float eps, const float* gain_q, const float* gain_k,
+                          float v_mult, void* q_out, long long q_stride, void* cache, const int* slots, int T, int H,
+                          int G, int D, int V, int page_size, int n_pages, int dtype, int* err, cudaStream_t stream) {
+  if (T <= 0) return SGLC_OK;
+  if (H <= 0 || G < 0 || D <= 0 || V <= 0 || dims < 0 || dims > D || dims % 2 != 0 || page_size <= 0 ||
+      norm_mode < 0 || norm_mode > 3 || (pairing != 0 && pairing != 1))
+    return SGLC_ERR_ARGUMENT;
+  if (norm_mode >= 2 && (!gain_q || (G > 0 && !gain_k))) return SGLC_ERR_ARGUMENT;
+  if (G > 0 && (!cache || !slots)) return SGLC_ERR_ARGUMENT;
+  if (dims > 0 && !freq) return SGLC_ERR_ARGUMENT;
+  if (D > ROT_MAX_DIM) return SGLC_ERR_UNSUPPORTED;
+  if (dtype == SGLC_F32)
+    return sglc_launch(qk_prep_kernel<float>, dim3(T), dim3(ROT_WARPS * 32), 0, stream, 1, true, x, x_stride, positions,
+                       freq, mult, dims, pairing, norm_mode, eps, gain_q, gain_k, v_mult, (float*)q_out, q_stride,
+                       (float*)cache, slots, T, H, G, D, V, page_size, n_pages, err);
+  if (dtype == SGLC_BF16)
+    return sglc_launch(qk_prep_kernel<__nv_bfloat16>, dim3(T), dim3(ROT_WARPS * 32), 0, stream, 1, true, x, x_stride,
+                       positions, freq, mult, dims, pairing, norm_mode, eps, gain_q, gain_k, v_mult,
+                       (__nv_bfloat16*)q_out, q_stride, (__nv_bfloat16*)cache, slots, T, H, G, D, V, page_size, n_pages,
+                       err);
+  return SGLC_ERR_ARGUMENT;
+}

@@ -1,2 +1,2 @@
 """Architectures.  Importing this package registers the built-in ones."""
-from . import buborax, gpt2, tukavik, zuretar  # noqa: F401
+from . import buborax, gpt2, lubavik, tukavik, zuretar  # noqa: F401

@@ -340,32 +340,69 @@ class RotaryAttention(Part):
     window.  `sink`: a learned score per head that joins the softmax's denominator once (it has no
     key and no value and is not scaled).  Query head i reads key/value head i / (n_heads / n_kv_heads).
     The cache keeps turned, normalised keys and plain values, a page's keys ahead of its values.
-    params: size, n_heads, n_kv_heads, head_dim, v_dim, scale, rotary (dims, base, scaling) or None,
-    qk_norm, eps, chunk, window, sink."""
+    Other forms of `qk_norm`, both BEFORE the turn and with learned gains: "head_gain": each head
+    divided by its root mean square times a gain of head_dim entries (`q_norm`, `k_norm`) that the
+    heads share; "row_gain": all query heads of a token divided by one root mean square over their
+    n_heads x head_dim entries times a gain of that size (`q_norm`), the key heads likewise
+    (`k_norm`).  The rotary params may ask for the pairing "neighbours".  `bias`: the four
+    projections have biases.  `own_kv` false: the layer has no key and value projections (nor
+    `k_norm`) and reads what another call cached (the plan's `cache_of`).  `out_mult`: a multiplier
+    of the mixer's result (the values are cached times it: the attention is linear in them).
+    params: size, n_heads, n_kv_heads, head_dim, v_dim, scale, rotary (dims, base, scaling, pairing) or
+    None, qk_norm, eps, chunk, window, sink, bias (default false), own_kv (default true), out_mult
+    (default 1)."""
 
     @classmethod
     def declare_weights(cls, params):
         E, H, G, D, V = (params[k] for k in ("size", "n_heads", "n_kv_heads", "head_dim", "v_dim"))
-        d = {"q_weight": WeightDecl((H * D, E), "matrix"), "k_weight": WeightDecl((G * D, E), "matrix"),
-             "v_weight": WeightDecl((G * V, E), "matrix"), "out_weight": WeightDecl((E, H * V), "residual_matrix")}
+        own, bias, norm = params.get("own_kv", True), params.get("bias", False), params.get("qk_norm")
+        d = {"q_weight": WeightDecl((H * D, E), "matrix"), "out_weight": WeightDecl((E, H * V), "residual_matrix")}
+        if own:
+            d.update({"k_weight": WeightDecl((G * D, E), "matrix"), "v_weight": WeightDecl((G * V, E), "matrix")})
+        if bias:
+            d.update({"q_bias": WeightDecl((H * D,), "bias"), "out_bias": WeightDecl((E,), "bias")})
+            if own:
+                d.update({"k_bias": WeightDecl((G * D,), "bias"), "v_bias": WeightDecl((G * V,), "bias")})
+        if norm in ("head_gain", "row_gain"):
+            d["q_norm"] = WeightDecl((D if norm == "head_gain" else H * D,), "norm_gain")
+            if own:
+                d["k_norm"] = WeightDecl((D if norm == "head_gain" else G * D,), "norm_gain")
         if params.get("sink"):
             d["sink"] = WeightDecl((H,), "bias")
         return d
 
     def load(self, tensors, store):
         from .registry import get_part
-        refs = [tensors[k] for k in ("q_weight", "k_weight", "v_weight")]
+        p = self.params
+        self.own = p.get("own_kv", True)
+        self.mult = float(p.get("out_mult", 1.0))
+        roles = ("q", "k", "v") if self.own else ("q",)
+        refs = [tensors[k + "_weight"] for k in roles]
         n = sum(r.tensor.shape[0] for r in refs)
         pad = (-n) % 8
+        bias = None
+        if p.get("bias", False):
+            brefs = [tensors[k + "_bias"] for k in roles]
+            bias = store.computed("+".join(r.name for r in brefs) + f"+{pad}", kind="vector", make=lambda: torch.cat(
+                [r.tensor.float() for r in brefs] + [torch.zeros(pad)]))
         self.qkv = Linear(store.computed("+".join(r.name for r in refs) + f"+{pad}", lambda: torch.cat(
-            [r.tensor.float() for r in refs] + [torch.zeros(pad, refs[0].tensor.shape[1])], 0)), None)
-        self.out = Linear(store.matrix(tensors["out_weight"]), None)
-        self.sink = store.vector(tensors["sink"]) if self.params.get("sink") else None
-        rot = self.params.get("rotary") or {"dims": 0, "base": 10000.0, "scaling": None}
+            [r.tensor.float() for r in refs] + [torch.zeros(pad, refs[0].tensor.shape[1])], 0)), bias)
+        out_bias = None
+        if p.get("bias", False):
+            ob, m = tensors["out_bias"], self.mult
+            out_bias = store.vector(ob) if m == 1.0 else store.computed(
+                f"{ob.name}*{m!r}", kind="vector", make=lambda: (ob.tensor.double() * m).float())
+        self.out = Linear(store.matrix(tensors["out_weight"]), out_bias)
+        self.sink = store.vector(tensors["sink"]) if p.get("sink") else None
+        rot = p.get("rotary") or {"dims": 0, "base": 10000.0, "scaling": None}
         self.rotary = get_part("position", "rotary")(rot, self.rt)
         self.rotary.load({}, store)
-        if self.rotary.pairing != "halves":
-            raise ValueError("rotary_attention: its kernel turns pairs (i, i + dims/2) only")
+        self.norm = p.get("qk_norm")
+        self.q_gain = store.vector(tensors["q_norm"]) if "q_norm" in tensors else None
+        self.k_gain = store.vector(tensors["k_norm"]) if "k_norm" in tensors else None
+        # the first kernel of this mixer serves its first form: unit-RMS heads behind a turn of halves
+        self.general = self.norm in ("head_gain", "row_gain") or self.rotary.pairing != "halves" or not self.own \
+            or self.mult != 1.0
 
     def cache_need(self):
         p = self.params
@@ -383,12 +420,22 @@ class RotaryAttention(Part):
         H, G, D, V = p["n_heads"], p["n_kv_heads"], p["head_dim"], p["v_dim"]
         T = h.shape[0]
         grp = ctx.group(cache.group)
+        if self.own != cache.write:
+            raise ValueError("rotary_attention: a layer with key and value projections owns its cache, one "
+                             "without reads another's")
         pre = ctx.alloc((T, self.qkv.out_size), torch.float32)
         self.qkv.forward(ctx, h, out=pre)
         q = ctx.alloc((T, H * D), self.rt.act_dtype)
-        ops.rotary_kv(ctx.columns(pre, 0, (H + G) * D + G * V), ctx.positions, self.rotary.frequencies,
-                      self.rotary.multiplier, self.rotary.dims, float(p["eps"]) if p.get("qk_norm") else None, q,
-                      cache.tensor, grp.slots, H, G, D, V, grp.page_size)
+        if self.general:
+            Gown = G if self.own else 0
+            ops.qk_prep(ctx.columns(pre, 0, H * D + Gown * (D + V)), ctx.positions, self.rotary.frequencies,
+                        self.rotary.multiplier, self.rotary.dims, self.rotary.pairing, self.norm, float(p["eps"]),
+                        self.q_gain, self.k_gain, q, cache.tensor if self.own else None,
+                        grp.slots if self.own else None, H, Gown, D, V, grp.page_size, v_mult=self.mult)
+        else:
+            ops.rotary_kv(ctx.columns(pre, 0, (H + G) * D + G * V), ctx.positions, self.rotary.frequencies,
+                          self.rotary.multiplier, self.rotary.dims, float(p["eps"]) if p.get("qk_norm") else None, q,
+                          cache.tensor, grp.slots, H, G, D, V, grp.page_size)
         o = ctx.alloc((T, H * V), self.rt.act_dtype)
         # a step of prompt portions only, keys and values of one size the tensor-core kernel takes (a
         # page is then its [2][G][page_size][D]): 128-query tiles on the tensor cores; every other
@@ -412,8 +459,12 @@ class SideBySideMixers(Part):
         mix(h) = (rms_norm(left(h)) * g_left + rms_norm(right(h)) * g_right) / 2.
     Each side keeps what it needs (the layer's cache need is the pair of theirs).  The halves are
     folded into the gains at load, and each side's norm adds straight into the 32-bit stream.
-    params: size, eps, left: (kind, params), right: (kind, params); weights: the sides' own under
-    `left.` / `right.`, and `left_out`, `right_out`."""
+    With `combine` "sum" the result is the plain sum of the sides' results, mix(h) = left(h) +
+    right(h), with no norms and no gains of its own (a side that is to count with a multiplier
+    takes it as its own parameter): the left side's last product writes, the right side's adds.
+    params: size, eps, left: (kind, params), right: (kind, params), combine ("normed_half_sum", the
+    default, or "sum"); weights: the sides' own under `left.` / `right.`, and (first form only)
+    `left_out`, `right_out`."""
 
     SIDES = ("left", "right")
 
@@ -429,7 +480,8 @@ class SideBySideMixers(Part):
         for side in cls.SIDES:
             klass, sub = cls._side_class(params, side)
             d.update({f"{side}.{role}": decl for role, decl in klass.declare_weights(sub).items()})
-            d[f"{side}_out"] = WeightDecl((params["size"],), "norm_gain")
+            if params.get("combine", "normed_half_sum") != "sum":
+                d[f"{side}_out"] = WeightDecl((params["size"],), "norm_gain")
         return d
 
     def __init__(self, params, runtime):
@@ -439,11 +491,16 @@ class SideBySideMixers(Part):
             klass, sub = self._side_class(params, side)
             self.sides.append(klass(sub, runtime))
         self.graph_safe = all(getattr(m, "graph_safe", True) for m in self.sides)
+        self.plain_sum = params.get("combine", "normed_half_sum") == "sum"
+        if params.get("combine", "normed_half_sum") not in ("normed_half_sum", "sum"):
+            raise ValueError(f"side_by_side: combine {params['combine']!r}; known: normed_half_sum, sum")
 
     def load(self, tensors, store):
         self.gains = []
         for side, part in zip(self.SIDES, self.sides):
             part.load({role[len(side) + 1:]: ref for role, ref in tensors.items() if role.startswith(side + ".")}, store)
+            if self.plain_sum:
+                continue
             ref = tensors[f"{side}_out"]
             self.gains.append(store.computed(ref.name + "/2", kind="vector", make=lambda r=ref: r.tensor.float() * 0.5))
 
@@ -459,6 +516,20 @@ class SideBySideMixers(Part):
 
     def forward(self, ctx, h, residual, cache, position=None, out=None):
         from ..csrc import ops
+        if self.plain_sum:
+            # the left side writes its result, the right side's last product adds to it
+            if out is None:
+                for part, binding in zip(self.sides, cache):
+                    mark = ctx.mark()
+                    part.forward(ctx, h, residual=residual, cache=binding, position=position)
+                    ctx.release(mark)
+                return residual
+            mark = ctx.mark()
+            self.sides[0].forward(ctx, h, residual=None, cache=cache[0], position=position, out=out)
+            ctx.release(mark)
+            self.sides[1].forward(ctx, h, residual=out, cache=cache[1], position=position)
+            ctx.release(mark)
+            return out
         if out is not None:
             raise ValueError("side_by_side adds into the residual stream; it has no separate output")
         T, E = h.shape[0], self.params["size"]

@@ -111,3 +111,67 @@ class ParallelSublayersBlock(Part):
             layer.ffn.forward(ctx, h, residual=x)
         ctx.release(mark)
         return x
+
+
+@register_part("block", "post_norm")
+class PostNormBlock(Part):
+    """A norm on each sublayer's result only; the sublayers read the stream itself:
+    x += norm1(mixer(x)); x += norm2(ffn(x)) (the second only if the layer has an `ffn`); then, if
+    the layer has a `side` sub-part (category stream_mix), x = side.finish(x) (an input that is made
+    from the stream and the step's tokens and added to it).  A sublayer's result is a 32-bit buffer;
+    the norm behind it sums it into the 32-bit stream.  In a runtime whose products take another
+    precision than the stream's, the stream's rows in that precision are written by the same launch
+    that last changed them (and kept in ctx.shared for the next layer of this kind), so that every
+    product reads rows that are up to date without a launch of its own.
+    params: last (the model's last layer: nobody reads the stream's rows in the products'
+    precision after it)."""
+
+    KEY = "post_norm_rows"
+
+    def workspace_per_token(self, layer):
+        act = 4 if self.rt.dtype == "float32" else 2
+        E = layer.norm1.params["size"]
+        inner = layer.mixer.workspace_per_token()
+        if "ffn" in layer.parts:
+            inner = max(inner, layer.ffn.workspace_per_token())
+        if "side" in layer.parts:
+            inner = max(inner, layer.side.workspace_per_token())
+        return (act + 4) * E + 256 + inner
+
+    def forward(self, ctx, x, layer, cache, position=None):
+        from ..csrc import ops
+        T, E = x.shape
+        mark = ctx.mark()
+        same = self.rt.act_dtype == torch.float32
+        if same:
+            h = x                              # the products read the stream as it is
+        else:
+            h = ctx.alloc((T, E), self.rt.act_dtype)
+            if ctx.shared.get(self.KEY) is not h:      # (the layer before did not leave them)
+                ops.cast_rows(x, h)
+        y = ctx.alloc((T, E), torch.float32)
+        inner = ctx.mark()
+        has_ffn, has_side = "ffn" in layer.parts, "side" in layer.parts
+        read_again = lambda more: None if same or not more else h
+        layer.mixer.forward(ctx, h, residual=None, cache=cache, position=position, out=y)
+        ctx.release(inner)
+        keep = has_ffn or has_side or not self.params.get("last")
+        self._add(ctx, layer.norm1, y, x, read_again(keep))
+        if has_ffn:
+            layer.ffn.forward(ctx, h, residual=None, out=y)
+            ctx.release(inner)
+            keep = has_side or not self.params.get("last")
+            self._add(ctx, layer.norm2, y, x, read_again(keep))
+        if has_side:
+            layer.side.finish(ctx, x, h=h, y=y, cast_out=read_again(not self.params.get("last")))
+            ctx.release(inner)
+        ctx.shared[self.KEY] = None if same or self.params.get("last") else h
+        ctx.release(mark)
+        return x
+
+    @staticmethod
+    def _add(ctx, norm, y, x, cast_out):
+        if cast_out is None:
+            norm.add_into(ctx, y, x)
+        else:
+            norm.add_into(ctx, y, x, then_cast=cast_out)

@@ -11,7 +11,7 @@ from .registry import register_part
 class MLP(Part):
     """residual += act(h·W_up + b_up)·W_down + b_down
     (reference src/gpt2.c:283-292; activation src/ops.c:233-241).
-    params: size, inner_size, activation ("gelu_tanh" | "gelu_erf" | "xielu"), bias,
+    params: size, inner_size, activation ("gelu_tanh" | "gelu_erf" | "xielu" | "relu2", the square of relu), bias,
     weight_layout ("conv1d" = [in,out] in the file, "linear" = [out,in]).
     "xielu" carries two numbers (p, q) of its own in a tensor `act_params`:
     act(z) = softplus(p) z^2 + z/2 for z > 0, (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2 otherwise."""
@@ -133,20 +133,34 @@ class RoutedExperts(Part):
     each expert's block of columns by the token's weight for it, which is zero for an expert not
     chosen; the down matrices, side by side, are one product whose contraction is the sum over
     experts.  A step does the same launches whatever the routing says.
-    params: size, inner_size (an expert's), n_experts, top, n_groups, keep."""
+    Other routings by parameter: `score` "softmax" (s = softmax over all experts instead of the
+    sigmoid), `renorm` (the chosen scores divided by their sum + 1e-20), `weight_scale` (a factor
+    of every weight), `correction` false (no such tensor).  `shared_inner_size`: one more expert of
+    that inner width (`shared_gate`, `shared_up`, `shared_down`) that every token uses with weight
+    1; its matrices lie behind the routed experts' in the same two products.
+    params: size, inner_size (an expert's), n_experts, top, n_groups, keep, score, renorm,
+    weight_scale, correction, shared_inner_size."""
 
     @classmethod
     def declare_weights(cls, params):
         E, F, X = params["size"], params["inner_size"], params["n_experts"]
-        d = {"router": WeightDecl((X, E), "matrix"), "correction": WeightDecl((X,), "bias")}
+        d = {"router": WeightDecl((X, E), "matrix")}
+        if params.get("correction", True):
+            d["correction"] = WeightDecl((X,), "bias")
         for e in range(X):
             d.update({f"gate_{e}": WeightDecl((F, E), "matrix"), f"up_{e}": WeightDecl((F, E), "matrix"),
                       f"down_{e}": WeightDecl((E, F), "residual_matrix")})
+        Fs = params.get("shared_inner_size")
+        if Fs:
+            d.update({"shared_gate": WeightDecl((Fs, E), "matrix"), "shared_up": WeightDecl((Fs, E), "matrix"),
+                      "shared_down": WeightDecl((E, Fs), "residual_matrix")})
         return d
 
     def load(self, tensors, store):
         X = self.params["n_experts"]
         gates, ups, downs = ([tensors[f"{k}_{e}"] for e in range(X)] for k in ("gate", "up", "down"))
+        if self.params.get("shared_inner_size"):
+            gates, ups, downs = gates + [tensors["shared_gate"]], ups + [tensors["shared_up"]], downs + [tensors["shared_down"]]
         self.gate_up = Linear(store.computed("+".join(r.name for r in gates + ups),
                                              lambda: torch.cat([r.tensor.float() for r in gates + ups], 0)), None)
         self.down = Linear(store.computed("|".join(r.name for r in downs),
@@ -155,13 +169,13 @@ class RoutedExperts(Part):
         pad = (-X) % 8
         self.router = Linear(store.computed(rw.name + f"+{pad}", lambda: torch.cat(
             [rw.tensor.float(), torch.zeros(pad, rw.tensor.shape[1])], 0)), None)
-        self.correction = store.vector(tensors["correction"])
+        self.correction = store.vector(tensors["correction"]) if "correction" in tensors else None
 
     def workspace_per_token(self):
         p = self.params
         act = 4 if self.rt.dtype == "float32" else 2
         X = p["n_experts"]
-        return act * 3 * X * p["inner_size"] + 4 * (2 * X + 8) + 8 * p["top"] + 1024
+        return act * 3 * (X * p["inner_size"] + int(p.get("shared_inner_size") or 0)) + 4 * (2 * X + 8) + 8 * p["top"] + 1024
 
     def forward(self, ctx, h, residual, out=None):
         from ..csrc import ops
@@ -172,9 +186,13 @@ class RoutedExperts(Part):
         dense = ctx.alloc((T, X), torch.float32)
         ids = ctx.alloc((T, top), torch.int32)
         wts = ctx.alloc((T, top), torch.float32)
-        ops.router(ctx.columns(z, 0, X), self.correction, dense, ids, wts, top, p.get("n_groups", 1), p.get("keep", 1))
-        gu = ctx.alloc((T, 2 * X * F), self.rt.act_dtype)
+        renorm = bool(p.get("renorm", False))
+        ops.router(ctx.columns(z, 0, X), self.correction, dense, ids, wts, top, p.get("n_groups", 1), p.get("keep", 1),
+                   renorm=renorm, weight_scale=float(p.get("weight_scale", 1.0)), score=p.get("score", "sigmoid"),
+                   renorm_eps=1e-20 if renorm else 0.0)
+        Fall = X * F + int(p.get("shared_inner_size") or 0)      # the shared expert's columns take weight 1
+        gu = ctx.alloc((T, 2 * Fall), self.rt.act_dtype)
         self.gate_up.forward(ctx, h, out=gu)
-        a = ctx.alloc((T, X * F), self.rt.act_dtype)
-        ops.gated_act(gu, a, weights=dense, per=F)
+        a = ctx.alloc((T, Fall), self.rt.act_dtype)
+        ops.gated_act(gu, a, weights=dense, per=F, n_weighted=X * F)
         return self.down.forward(ctx, a, out=out, residual=residual)

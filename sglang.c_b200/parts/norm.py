@@ -23,7 +23,12 @@ class LayerNorm(Part):
         return d
 
     def load(self, tensors, store):
-        self.weight = store.vector(tensors["weight"])
+        ref = tensors["weight"]
+        if self.params.get("one_plus"):
+            # a gain stored around zero: the kernels multiply by 1 + w, formed once
+            self.weight = store.computed(ref.name + "+1", kind="vector", make=lambda: ref.tensor.float() + 1.0)
+        else:
+            self.weight = store.vector(ref)
         self.bias = store.vector(tensors["bias"]) if "bias" in tensors else None
 
     @property
@@ -39,12 +44,25 @@ class LayerNorm(Part):
                           src_rows=rows, groups=self.groups)
         return out
 
-    def add_into(self, ctx, y, residual, mix=None, then=None):
+    def add_into(self, ctx, y, residual, mix=None, then=None, then_cast=None):
         """residual += norm(y): the norm behind a sublayer, summed into the 32-bit stream.  In the
         same launch, if asked: `mix` = (hist, n_terms, weights), the depth mix of the summed rows
         (see ops.depth_mix), and `then` = (norm part, out): out = that norm of the rows as they
         then are (the norm ahead of the next sublayer).  Returns which of the two it did: a norm
-        with a bias, or a source that is not 32-bit, leaves them to the caller."""
+        with a bias, or a source that is not 32-bit, leaves them to the caller.
+        `then_cast` (instead of `then`): a buffer that takes the summed rows in its own precision,
+        for a next sublayer that reads the stream itself; always done (in the same launch where the
+        fused kernel serves, by a second one else)."""
+        if then_cast is not None:
+            if self.groups == 1 and self.bias is None and y.dtype == residual.dtype \
+                    and y.shape[0] == residual.shape[0] and residual.is_contiguous():
+                ops.norm_add_tail(y, self.weight, float(self.params["eps"]), residual, form=self.form,
+                                  then=(None, 0.0, "copy", then_cast))
+            else:
+                ops.norm_rows(y, self.weight, self.bias, float(self.params["eps"]), residual[:y.shape[0]],
+                              form=self.form, add=True, groups=self.groups)
+                ops.cast_rows(residual[:y.shape[0]], then_cast)
+            return True
         fused = self.groups == 1 and (then is None or then[0].groups == 1) \
             and y.dtype == residual.dtype and self.bias is None and (then is None or then[0].bias is None) \
             and y.shape[0] == residual.shape[0] and residual.is_contiguous() and (mix is not None or then is not None)
@@ -67,7 +85,8 @@ class LayerNorm(Part):
 class RMSNorm(LayerNorm):
     """y = x / sqrt(mean(x^2) + eps) * weight, eps inside the root, statistics in 32-bit.
     params: size, eps, groups (default 1; more: each of so many equal consecutive parts of the row is
-    divided by its own root mean square)."""
+    divided by its own root mean square), one_plus (default false; true: the file's tensor is stored
+    around zero and the gain is 1 + it)."""
 
     form = "rms"
 

@@ -13,7 +13,9 @@ from typing import Dict, List, Optional, Tuple
 
 @dataclass(frozen=True)
 class WeightDecl:
-    """One tensor a part needs.  `shape` is the shape in the file.  `init`
+    """One tensor a part needs.  `shape` is the shape in the file; a size <= 0 is free (the
+    file's tensor decides it, e.g. the rank of a low-rank pair) and -n says that a tensor made at
+    random takes n there.  `init`
     names the tensor's role for random initialisation: "matrix",
     "residual_matrix" (a projection back into the residual stream),
     "embedding", "bias", "norm_gain", "norm_bias", "conv_taps" (the taps of a short convolution

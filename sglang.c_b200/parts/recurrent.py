@@ -256,3 +256,150 @@ class RowGatedState(Part):
         z = ctx.alloc((T, H * V), self.rt.act_dtype)
         ops.gated_norm(o, None, self.norm, z, H, V, float(p["eps"]), "none")
         return self.out.forward(ctx, z, out=out, residual=residual)
+
+
+@register_part("mixer", "gated_linear_attention")
+class GatedLinearAttention(Part):
+    """Linear attention with a learned decay per key channel and token:
+        q = h Wq^T * dim^(-1/2), k = h Wk^T (n_heads x dim), v = h Wv^T (n_heads x v_dim);
+        a = sigmoid(z)^(1/tau), z = (h Wa1^T) Wa2^T + ba, laid out n_heads x dim (a low-rank product);
+        per head S <- diag(a_t) S + k_t v_t^T, o_t = S^T q_t.
+    Each head's o is divided by its root mean square (eps) times a gain of v_dim entries that the heads
+    share; the heads side by side are multiplied by silu(h Wg^T) and projected.  q, k, v, the gate and
+    the decay's first factor are one product with a 32-bit result; the decay's second factor is a
+    small product of its own (its input in the activation precision, its bias in the epilogue, a
+    32-bit result); decays, state and norm are 32-bit.  S starts at zero and is carried per request.
+    params: size, n_heads, dim, v_dim, tau, eps, out_mult (a multiplier of the mixer's result, default
+    1, folded into the norm's gain), decay_rank (only for weights made at random: the rank of the
+    decay's two factors is what the file's tensors have)."""
+
+    @classmethod
+    def declare_weights(cls, params):
+        E, H, D, V = (params[k] for k in ("size", "n_heads", "dim", "v_dim"))
+        r = -int(params.get("decay_rank", 16))      # free: the file's tensors decide the rank
+        return {"q_weight": WeightDecl((H * D, E), "matrix"), "k_weight": WeightDecl((H * D, E), "matrix"),
+                "v_weight": WeightDecl((H * V, E), "matrix"), "gate_weight": WeightDecl((H * V, E), "matrix"),
+                "decay_down": WeightDecl((r, E), "matrix"), "decay_up": WeightDecl((H * D, r), "matrix"),
+                "decay_bias": WeightDecl((H * D,), "bias"), "norm": WeightDecl((V,), "norm_gain"),
+                "out_weight": WeightDecl((E, H * V), "residual_matrix")}
+
+    def load(self, tensors, store):
+        p = self.params
+        H, D, V = p["n_heads"], p["dim"], p["v_dim"]
+        refs = [tensors[k] for k in ("q_weight", "k_weight", "v_weight", "gate_weight", "decay_down")]
+        self.rank = refs[-1].tensor.shape[0]
+        n = 2 * H * D + 2 * H * V + self.rank
+        pad = (-n) % 8
+        self.inp = Linear(store.computed("+".join(r.name for r in refs) + f"+{pad}", lambda: torch.cat(
+            [r.tensor.float() for r in refs] + [torch.zeros(pad, refs[0].tensor.shape[1])], 0)), None)
+        self.up = Linear(store.matrix(tensors["decay_up"]), store.vector(tensors["decay_bias"]))
+        m = float(p.get("out_mult", 1.0))
+        g = tensors["norm"]
+        self.norm = store.vector(g) if m == 1.0 else store.computed(
+            f"{g.name}*{m!r}", kind="vector", make=lambda: (g.tensor.double() * m).float())
+        self.out = Linear(store.matrix(tensors["out_weight"]), None)
+
+    def cache_need(self):
+        p = self.params
+        return CacheNeed.state((p["n_heads"], p["dim"], p["v_dim"]), "float32")
+
+    def workspace_per_token(self):
+        p = self.params
+        H, D, V = p["n_heads"], p["dim"], p["v_dim"]
+        act = 4 if self.rt.dtype == "float32" else 2
+        r = getattr(self, "rank", 64)
+        return 4 * (2 * H * D + 2 * H * V + r + 8) + act * r + 4 * H * D + 4 * H * V + act * H * V + 2048
+
+    def forward(self, ctx, h, residual, cache, position=None, out=None):
+        p = self.params
+        H, D, V, r = p["n_heads"], p["dim"], p["v_dim"], self.rank
+        T = h.shape[0]
+        pre = ctx.alloc((T, self.inp.out_size), torch.float32)
+        self.inp.forward(ctx, h, out=pre)
+        c_v, c_g, c_a = 2 * H * D, 2 * H * D + H * V, 2 * H * D + 2 * H * V
+        low = ctx.columns(pre, c_a, c_a + r)
+        if self.rt.act_dtype != torch.float32:
+            low_a = ctx.alloc((T, r), self.rt.act_dtype)
+            ops.cast_rows(low, low_a)
+            low = low_a
+        z = ctx.alloc((T, H * D), torch.float32)
+        self.up.forward(ctx, low, out=z)
+        o = ctx.alloc((T, H * V), torch.float32)
+        ops.matrix_state("row_decay", ctx.columns(pre, 0, H * D), ctx.columns(pre, H * D, 2 * H * D),
+                         ctx.columns(pre, c_v, c_g), o, cache.tensor, ctx.q_start, ctx.state_slots, ctx.R, H, H, D, V,
+                         row_z=z, tau=float(p["tau"]), q_scale=float(D) ** -0.5)
+        y = ctx.alloc((T, H * V), self.rt.act_dtype)
+        ops.gated_norm(o, ctx.columns(pre, c_g, c_a), self.norm, y, H, V, float(p["eps"]), "silu")
+        return self.out.forward(ctx, y, out=out, residual=residual)
+
+
+@register_part("mixer", "mlstm")
+class MatrixMemory(Part):
+    """The matrix memory of xLSTM (mLSTM) with exponential gates and a running maximum:
+        q = h Wq^T * dim^(-1/2), k = h Wk^T (n_heads x dim), v = h Wv^T (n_heads x v_dim);
+        per head the log gates i = cap tanh((h wi + bi) / cap), f = log sigmoid(cap tanh((h wf + bf) / cap));
+        m_t = max(f + m_(t-1), i)                                   (m starts at 0)
+        S_t = exp(f + m_(t-1) - m_t) S_(t-1) + exp(i - m_t) k v^T,   n_t likewise with k alone;
+        o = S_t^T q / (max(|n_t . q|, exp(-m_t)) + 1e-6).
+    Each head's o is divided by its root mean square (eps); the heads side by side are multiplied by a
+    gain of n_heads x v_dim entries and by sigmoid(h Wg^T), then projected.  All projections are one
+    product with a 32-bit result (the gates' biases in its epilogue); gates, maxima, state and norm
+    are 32-bit.  Kept per request: S with n as one more column behind it ([n_heads, dim, v_dim + 1]),
+    and m ([n_heads]); both start at zero.
+    params: size, n_heads, dim, v_dim, gate_cap, eps."""
+
+    @classmethod
+    def declare_weights(cls, params):
+        E, H, D, V = (params[k] for k in ("size", "n_heads", "dim", "v_dim"))
+        return {"q_weight": WeightDecl((H * D, E), "matrix"), "k_weight": WeightDecl((H * D, E), "matrix"),
+                "v_weight": WeightDecl((H * V, E), "matrix"), "gate_weight": WeightDecl((H * V, E), "matrix"),
+                "in_gate_weight": WeightDecl((H, E), "matrix"), "in_gate_bias": WeightDecl((H,), "bias"),
+                "forget_weight": WeightDecl((H, E), "matrix"), "forget_bias": WeightDecl((H,), "bias"),
+                "norm": WeightDecl((H * V,), "norm_gain"), "out_weight": WeightDecl((E, H * V), "residual_matrix")}
+
+    def load(self, tensors, store):
+        p = self.params
+        H, D, V = p["n_heads"], p["dim"], p["v_dim"]
+        refs = [tensors[k] for k in ("q_weight", "k_weight", "v_weight", "gate_weight", "in_gate_weight", "forget_weight")]
+        n = 2 * H * D + 2 * H * V + 2 * H
+        pad = (-n) % 8
+        self.inp_w = store.computed("+".join(r.name for r in refs) + f"+{pad}", lambda: torch.cat(
+            [r.tensor.float() for r in refs] + [torch.zeros(pad, refs[0].tensor.shape[1])], 0))
+        bi, bf = tensors["in_gate_bias"], tensors["forget_bias"]
+        bias = store.computed(f"0+{bi.name}+{bf.name}+{pad}", kind="vector", make=lambda: torch.cat(
+            [torch.zeros(n - 2 * H), bi.tensor.float(), bf.tensor.float(), torch.zeros(pad)]))
+        self.inp = Linear(self.inp_w, bias)
+        self.norm = store.vector(tensors["norm"])
+        self.out = Linear(store.matrix(tensors["out_weight"]), None)
+
+    def cache_need(self):
+        p = self.params
+        return (CacheNeed.state((p["n_heads"], p["dim"], p["v_dim"] + 1), "float32"),
+                CacheNeed.state((p["n_heads"],), "float32"))
+
+    def workspace_per_token(self):
+        p = self.params
+        H, D, V = p["n_heads"], p["dim"], p["v_dim"]
+        act = 4 if self.rt.dtype == "float32" else 2
+        return 4 * (2 * H * D + 2 * H * V + 2 * H + 8) + 12 * H + 4 * H * (V + 1) + act * H * V + 2048
+
+    def forward(self, ctx, h, residual, cache, position=None, out=None):
+        p = self.params
+        H, D, V = p["n_heads"], p["dim"], p["v_dim"]
+        T = h.shape[0]
+        state, maxima = cache
+        pre = ctx.alloc((T, self.inp.out_size), torch.float32)
+        self.inp.forward(ctx, h, out=pre)
+        c_v, c_g, c_i = 2 * H * D, 2 * H * D + H * V, 2 * H * D + 2 * H * V
+        gates = ctx.alloc((T, 2 * H), torch.float32)
+        m_run = ctx.alloc((T, H), torch.float32)
+        ops.stabilized_gates(ctx.columns(pre, c_i, c_i + H), ctx.columns(pre, c_i + H, c_i + 2 * H), float(p["gate_cap"]),
+                             gates, m_run, maxima.tensor, ctx.q_start, ctx.state_slots, ctx.R, H)
+        o = ctx.alloc((T, H * (V + 1)), torch.float32)
+        ops.matrix_state("gated", ctx.columns(pre, 0, H * D), ctx.columns(pre, H * D, 2 * H * D),
+                         ctx.columns(pre, c_v, c_g), o, state.tensor, ctx.q_start, ctx.state_slots, ctx.R, H, H, D, V + 1,
+                         gates=gates, q_scale=float(D) ** -0.5, ones_col=True)
+        y = ctx.alloc((T, H * V), self.rt.act_dtype)
+        ops.gated_norm(o, ctx.columns(pre, c_g, c_i), self.norm, y, H, V, float(p["eps"]), "sigmoid", o_pitch=V + 1,
+                       m_run=m_run)
+        return self.out.forward(ctx, y, out=out, residual=residual)

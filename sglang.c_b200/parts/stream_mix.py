@@ -76,3 +76,57 @@ class InputReentry(Part):
         ops.cast_rows(x, ctx.columns(rows, 0, self.params["size"]))
         ctx.rt.gemm(rows, self.inp.weight, self.steps[t], out=x, few_ok=ctx.few_token_ok)
         return x
+
+
+@register_part("stream_mix", "token_gated_input")
+class TokenGatedInput(Part):
+    """An input from a second token table, gated by the stream and added to it behind a norm:
+        e = table[token][index * dim : (index + 1) * dim]      (the table holds every layer's part)
+        g = gelu_tanh(Wg x) * e;   y = Wp g;   x += y / sqrt(mean(y^2) + eps) * gain
+    Two small products with 32-bit results, the gate and gather between them, and the norm that
+    sums into the 32-bit stream.  params: size, dim, index, n_layers, vocab_size, eps."""
+
+    @classmethod
+    def declare_weights(cls, params):
+        E, d = params["size"], params["dim"]
+        return {"table": WeightDecl((params["vocab_size"], params["n_layers"] * d), "embedding"),
+                "gate_weight": WeightDecl((d, E), "matrix"), "proj_weight": WeightDecl((E, d), "residual_matrix"),
+                "norm": WeightDecl((E,), "norm_gain")}
+
+    def load(self, tensors, store):
+        from .linear import Linear
+        self.table = store.matrix(tensors["table"])
+        self.gate = Linear(store.matrix(tensors["gate_weight"]), None)
+        self.proj = Linear(store.matrix(tensors["proj_weight"]), None)
+        self.gain = store.vector(tensors["norm"])
+
+    def workspace_per_token(self):
+        act = 4 if self.rt.dtype == "float32" else 2
+        return (4 + act) * self.params["dim"] + 512
+
+    def finish(self, ctx, x, h=None, y=None, cast_out=None):
+        """x += the gated input.  h: the stream's rows in the products' precision, if the caller has
+        them; y: a 32-bit buffer [T, size] to use; cast_out: a buffer that takes the new rows in its
+        own precision (same launch as the sum)."""
+        p = self.params
+        T, d = x.shape[0], p["dim"]
+        if h is None:
+            if self.rt.act_dtype == torch.float32:
+                h = x
+            else:
+                h = ctx.alloc((T, p["size"]), self.rt.act_dtype)
+                ops.cast_rows(x, h)
+        if y is None:
+            y = ctx.alloc((T, p["size"]), torch.float32)
+        z = ctx.alloc((T, d), torch.float32)
+        self.gate.forward(ctx, h, out=z)
+        g = ctx.alloc((T, d), self.rt.act_dtype)
+        ops.gated_gather(z, ctx.tokens, self.table, p["index"] * d, g, err_flag=ctx.err_flag)
+        self.proj.forward(ctx, g, out=y)
+        if cast_out is not None and x.is_contiguous():
+            ops.norm_add_tail(y, self.gain, float(p["eps"]), x, form="rms", then=(None, 0.0, "copy", cast_out))
+        else:
+            ops.norm_rows(y, self.gain, None, float(p["eps"]), x[:T], form="rms", add=True)
+            if cast_out is not None:
+                ops.cast_rows(x[:T], cast_out)
+        return x

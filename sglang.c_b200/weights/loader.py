@@ -152,8 +152,11 @@ def load_checked(plan, model_dir):
                 missing.append(name)
                 continue
             found[name] = actual
-            if tuple(f.shape(actual)) != tuple(decl.shape):
-                wrong.append(f"{actual}: file has {list(f.shape(actual))}, model needs {list(decl.shape)}")
+            have = tuple(f.shape(actual))
+            # (a declared size <= 0 is free: the file's tensor decides it)
+            if len(have) != len(decl.shape) or any(d > 0 and d != h for d, h in zip(decl.shape, have)):
+                wrong.append(f"{actual}: file has {list(have)}, model needs "
+                             f"{[d if d > 0 else 'any' for d in decl.shape]}")
             elif decl.kind == "float" and not f.dtype(actual).is_floating_point:
                 wrong.append(f"{actual}: file has {f.dtype(actual)}, model needs a floating-point tensor")
             elif decl.kind == "int" and f.dtype(actual).is_floating_point:

@@ -37,7 +37,7 @@ def _stream(seed, name):
 
 def random_tensor(seed, name, decl, scheme, n_layers, vocab_size=None):
     rng = _stream(seed, name)
-    shape = tuple(decl.shape)
+    shape = tuple(d if d > 0 else max(-d, 1) for d in decl.shape)     # (a free size takes its stand-in)
     if decl.kind == "int":
         hi = vocab_size or 2
         return torch.from_numpy(rng.integers(0, hi, size=shape, dtype=np.int32))
