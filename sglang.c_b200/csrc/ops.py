@@ -1031,7 +1031,7 @@ def qk_prep(x, positions, freq, mult, dims, pairing, norm, eps, gain_q, gain_k, 
                 or cache.numel() != n_pages * G * page_size * (dim + v_dim):
             raise KernelError(f"qk_prep: cache {tuple(cache.shape)} does not fit {G} heads of {dim}+{v_dim}, or its "
                               "dtype is not the queries'")
-    want = {2: (dim, dim), 3: (n_heads * dim, G * dim)}.get(mode)
+    want = {2: (dim, dim if G else 0), 3: (n_heads * dim, G * dim)}.get(mode)
     if want is not None:
         for g, n, nm in ((gain_q, want[0], "queries"), (gain_k, want[1], "keys")):
             if n and (g is None or g.dtype != torch.float32 or g.numel() != n or not g.is_contiguous()):

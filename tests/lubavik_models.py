@@ -87,6 +87,37 @@ LUB = {"A": LUB_A, "B": LUB_B, "C": LUB_C}
 PAGE = {"A": 16, "B": 16, "C": 8}
 
 
+def _rewrite(src, out, store_dtype, change, cfg_change=None):
+    """The folder `src` (32-bit) written again as `out` with change(name, array) applied to every tensor."""
+    import plain_lubavik
+    from sglang_c_b200.weights.safetensors_io import write_safetensors
+    cfg, w = plain_lubavik.read_model_dir(src)
+    cfg = copy.deepcopy(cfg)
+    if cfg_change is not None:
+        cfg_change(cfg)
+    tensors = {}
+    for k, v in w.items():
+        t = torch.from_numpy(np.ascontiguousarray(change(k, np.array(v, dtype=np.float32)), dtype=np.float32))
+        tensors[k] = t.to(torch.bfloat16) if (store_dtype == "bfloat16" and t.dim() >= 2) else t
+    os.makedirs(out, exist_ok=True)
+    with open(os.path.join(out, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    write_safetensors(os.path.join(out, "model.safetensors"), tensors, metadata={"format": "pt"})
+    return out
+
+
+def _lively(k, a):
+    """Random weights of the usual small size leave two things degenerate here: a token table of
+    entries around 0.02 puts the first layer's read-outs far below the eps of its norms, and router
+    logits that are all alike make every choice a close call, which rounding decides.  So the token
+    table is made of entries around one and the routers' rows are spread out."""
+    if k == "embed":
+        return a * 50.0
+    if k.endswith(".mlp.router"):
+        return a * 12.0
+    return a
+
+
 def make_dir(tmp, name, store_dtype="float32", seed=None):
     from sglang_c_b200.config import resolve_architecture
     from sglang_c_b200.weights import write_random_model
@@ -94,8 +125,9 @@ def make_dir(tmp, name, store_dtype="float32", seed=None):
     arch = resolve_architecture(d)
     out = os.path.join(str(tmp), f"lub_{name}_{store_dtype}")
     if not os.path.exists(os.path.join(out, "model.safetensors")):
-        write_random_model(out, arch, arch.config_class.from_dict(d), seed if seed is not None else 700 + ord(name),
-                           scheme="varied", store_dtype=store_dtype)
+        raw = write_random_model(out + "_raw", arch, arch.config_class.from_dict(d),
+                                 seed if seed is not None else 700 + ord(name), scheme="varied", store_dtype="float32")
+        _rewrite(raw, out, store_dtype, _lively)
     return out
 
 
@@ -105,32 +137,25 @@ def make_sharp_dir(tmp, name, store_dtype="float32"):
     page or let in across a chunk's edge then moves the logits by far more than rounding), sinks
     raised so that they carry weight, the linear attention's decays close to one (the decays' biases
     raised: the state remembers hundreds of tokens) and the matrix memory's forget gates close to one."""
-    import plain_lubavik
-    from sglang_c_b200.weights.safetensors_io import write_safetensors
     base = make_dir(tmp, name, "float32")
     out = os.path.join(str(tmp), f"lub_sharp_{name}_{store_dtype}")
     if os.path.exists(os.path.join(out, "model.safetensors")):
         return out
-    cfg, w = plain_lubavik.read_model_dir(base)
-    cfg = copy.deepcopy(cfg)
-    for entry in cfg["layers"]:
-        if entry["type"] == "parallel":
-            entry["mixer"]["left"]["scale"] *= 6.0
-        elif entry["type"] == "attention":
-            entry["mixer"]["scale"] *= 6.0
-    tensors = {}
-    for k, v in w.items():
-        a = np.array(v, dtype=np.float32)
+
+    def sharper(cfg):
+        for entry in cfg["layers"]:
+            if entry["type"] == "parallel":
+                entry["mixer"]["left"]["scale"] *= 6.0
+            elif entry["type"] == "attention":
+                entry["mixer"]["scale"] *= 6.0
+
+    def change(k, a):
         if k.endswith(".mix.right.a2.b"):
-            a = a + 5.0
-        elif k.endswith(".mix.f.b"):
-            a = a + 4.0
-        elif k.endswith(".mix.sink"):
-            a = a + 1.5
-        t = torch.from_numpy(a)
-        tensors[k] = t.to(torch.bfloat16) if (store_dtype == "bfloat16" and t.dim() >= 2) else t
-    os.makedirs(out, exist_ok=True)
-    with open(os.path.join(out, "config.json"), "w") as f:
-        json.dump(cfg, f)
-    write_safetensors(os.path.join(out, "model.safetensors"), tensors, metadata={"format": "pt"})
-    return out
+            return a + 5.0
+        if k.endswith(".mix.f.b"):
+            return a + 4.0
+        if k.endswith(".mix.sink"):
+            return a + 1.5
+        return a
+
+    return _rewrite(base, out, store_dtype, change, sharper)
