@@ -18,7 +18,7 @@ requests) over its time, against the measured copy bandwidth; `points` has decod
 at batch 1 and 64, the true 32-bit path and the prefill through the C interface;
 `kernels` says where a decode and a
 prefill step's time goes, kernel by kernel.  `--full` adds medium and XL layer
-sizes and the mixed workload to `points`.  `--compare tukavik` (or `zuretar`, or `buborax`, each of which adds its design as one more column) measures,
+sizes and the mixed workload to `points`.  `--compare tukavik` (or `zuretar`, or `buborax`, each of which adds its design as one more column; `lubavik`: that design beside Zuretar, the closest one) measures,
 instead of all this, a Tukavik model beside the GPT-2 model of the same layer sizes.
 """
 import argparse
@@ -827,6 +827,83 @@ def buborax_step_bytes(cfg, batch, context, prompt_tokens):
     return out
 
 
+def lubavik_config(base, n_layer):
+    """A Lubavik model with the layer sizes of a GPT-2 model: the same width, depth, head size (64) and
+    vocabulary.  Layers in fours: a matrix memory with exponential gates (the model's heads, keys and
+    values of 64) with a dense feed-forward of GPT-2's inner width under a squared relu; softmax
+    attention with sinks (the model's heads over a quarter as many key/value heads, full rotation) with
+    a mixture of 8 experts of a sixth of that width, 2 chosen, and a shared expert of the same width;
+    chunked attention (chunks of 256) beside a gated linear attention of a quarter of the heads (decays
+    of rank 16), with the experts; and attention that reads the second layer's keys and values, with
+    the dense feed-forward.  Every layer ends with a token-gated input of 64 entries."""
+    E, H, I = base["n_embd"], base["n_head"], base["n_inner"]
+    dense = {"kind": "dense", "ff": I}
+    fe = max(64, (I // 6) // 64 * 64)
+    moe = {"kind": "moe", "expert": {"ff": fe}, "router": {"experts": 8, "top": 2, "scale": 2.0}, "shared": {"ff": fe}}
+    hq = max(1, H // 4)
+    rot = {"base": 10000.0, "dims": 64}
+    attn = {"heads": H, "kv_heads": hq, "dim": 64, "vdim": 64, "scale": 0.125, "rot": rot}
+    par = {"left": dict(attn, mask={"size": 256}), "right": {"heads": hq, "dim": 64, "vdim": 64, "tau": 16.0},
+           "left_scale": 0.8, "right_scale": 0.5}
+    layers = []
+    for i in range(n_layer):
+        if i % 4 == 0:
+            layers.append({"type": "mlstm", "mixer": {"heads": H, "dim": 64, "vdim": 64, "gate_cap": 15.0}, "mlp": dense})
+        elif i % 4 == 1:
+            layers.append({"type": "attention", "mixer": attn, "mlp": moe})
+        elif i % 4 == 2:
+            layers.append({"type": "parallel", "mixer": par, "mlp": moe})
+        else:
+            layers.append({"type": "attention", "mixer": dict(attn, kv_from=i - 2), "mlp": dense})
+    return {"architecture": "Lubavik", "vocab": base["vocab_size"], "width": E, "norm": {"eps": 1e-6},
+            "token_side": {"dim": 64}, "layers": layers, "max_positions": base["n_positions"]}
+
+
+def lubavik_step_bytes(cfg, batch, context, prompt_tokens):
+    """What the kernels that this design adds or extends must move in a step (32-bit projections, states
+    and read-outs; bfloat16 activations and cache): {decode | prefill: {kernel label: bytes}}."""
+    E, d = cfg["width"], cfg["token_side"]["dim"]
+    out = {}
+    for name, T, R in (("decode", batch, batch), ("prefill", prompt_tokens, 2)):
+        prep = state = gates = gnorm = attn = gact = tail = gather = route = 0
+        for layer in cfg["layers"]:
+            m = layer["mixer"]
+            tail += T * E * (4 + 8 + 2)                        # the sublayer's result, the stream read and written, the copy
+            if layer["type"] == "mlstm":
+                H, D, V = m["heads"], m["dim"], m["vdim"]
+                gates += T * H * (8 + 12) + R * H * 8
+                state += R * H * D * (V + 1) * 8 + T * (2 * H * D + H * V + 2 * H + H * (V + 1)) * 4
+                gnorm += T * H * ((V + 1) * 4 + V * 4 + V * 2)
+            else:
+                a = m["left"] if layer["type"] == "parallel" else m
+                G = 0 if "kv_from" in a else a["kv_heads"]
+                row = a["heads"] * a["dim"] + G * (a["dim"] + a["vdim"])
+                prep += T * row * (4 + 2)
+                chunk = a.get("mask", {}).get("size")
+                kv = a["kv_heads"] * (a["dim"] + a["vdim"]) * 2
+                if name == "decode":
+                    seen = min(context, chunk) if chunk else context
+                    attn += T * seen * kv + T * a["heads"] * (a["dim"] + a["vdim"]) * 2
+                if layer["type"] == "parallel":
+                    ri = m["right"]
+                    hd, hv = ri["heads"] * ri["dim"], ri["heads"] * ri["vdim"]
+                    state += R * ri["heads"] * ri["dim"] * ri["vdim"] * 8 + T * (3 * hd + 2 * hv) * 4
+                    gnorm += T * hv * (8 + 2)
+            mlp = layer["mlp"]
+            if mlp:
+                tail += T * E * (4 + 8 + 2)
+                if mlp["kind"] == "moe":
+                    X = mlp["router"]["experts"]
+                    gact += T * (mlp["expert"]["ff"] * X + mlp["shared"]["ff"]) * 6 + T * X * 4
+                    route += T * X * 8 + T * mlp["router"]["top"] * 8
+            tail += T * E * (4 + 8 + 2)
+            gather += T * d * (4 + 2 + 2)
+        out[name] = {"qk_prep": prep, "matrix_state": state, "stabilized_gates": gates, "gated_norm": gnorm,
+                     "attention_ext": attn, "gated_act": gact, "norm_add_tail": tail, "gated_gather": gather,
+                     "router": route}
+    return out
+
+
 DESIGNS = {"tukavik": (tukavik_config, tukavik_step_bytes,
                        {"mingru_scan": "mingru_scan", "norm_rows": "norm_rows", "depth_mix": "depth_mix",
                         "attention_decode_shared": "attention_shared"}),
@@ -834,7 +911,10 @@ DESIGNS = {"tukavik": (tukavik_config, tukavik_step_bytes,
                        {k: k for k in ("short_conv", "matrix_state", "gated_norm", "rotary_kv", "attention_ext", "gated_act")}),
            "buborax": (buborax_config, buborax_step_bytes,
                        {k: k for k in ("matrix_state", "gated_norm", "latent_rope", "talk_prep", "talk_attention",
-                                       "gated_act", "norm_rows", "cast_rows")})}
+                                       "gated_act", "norm_rows", "cast_rows")}),
+           "lubavik": (lubavik_config, lubavik_step_bytes,
+                       {k: k for k in ("qk_prep", "matrix_state", "stabilized_gates", "gated_norm", "attention_ext",
+                                       "gated_act", "norm_add_tail", "gated_gather", "router")})}
 
 
 def compare_designs(designs, sizes, steps, warmup, pk):
@@ -963,7 +1043,7 @@ def main():
     ap.add_argument("--only", default=None, choices=["decode", "prefill", "fp32"],
                     help="a handful of steps of one kind and nothing else (what a profiler is pointed at): "
                          "decode steps at batch 8, prefill steps of 2 x 1,024 tokens, or both on the 32-bit path")
-    ap.add_argument("--compare", default=None, choices=["tukavik", "zuretar", "buborax"],
+    ap.add_argument("--compare", default=None, choices=["tukavik", "zuretar", "buborax", "lubavik"],
                     help="nothing of the above: decode and prefill of a model of this design beside the GPT-2 model "
                          "of equal layer sizes (--model, or small and medium with --full), with both kernel tables")
     args = ap.parse_args()
@@ -984,7 +1064,7 @@ def main():
         clocks = ClockSampler()
         clocks.start()
         designs = {"tukavik": ["tukavik"], "zuretar": ["tukavik", "zuretar"],
-                   "buborax": ["tukavik", "zuretar", "buborax"]}[args.compare]
+                   "buborax": ["tukavik", "zuretar", "buborax"], "lubavik": ["zuretar", "lubavik"]}[args.compare]
         res = compare_designs(designs, ["small", "medium"] if args.full else [args.model], steps, warmup, pk)
         print(json.dumps({"metric": f"decode and prefill tok/s, {' and '.join(d.capitalize() for d in designs)} beside "
                                     "GPT-2 at equal layer sizes (Python engine)",

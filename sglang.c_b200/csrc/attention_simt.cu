@@ -41,7 +41,8 @@ attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restri
                       const int* __restrict__ token_req, const int* __restrict__ positions,
                       TO* __restrict__ out, int o_stride, int T, int H, int Hkv, int D, int page_size,
                       float scale, int window, int n_pages, int* err, int kv_shared,
-                      int DV_arg, int chunk, const float* __restrict__ sinks) {
+                      int DV_arg, int chunk, const float* __restrict__ sinks, int n_splits,
+                      float* __restrict__ part_ws) {
   const int DV = EXT ? DV_arg : D;
   extern __shared__ __align__(16) float smem[];
   __shared__ int s_req[W], s_lo[W], s_pos[W];
@@ -91,7 +92,15 @@ attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restri
       pos_max = max(pos_max, s_pos[w]);
     }
     const int* bt = block_table + (size_t)rl * bt_stride;
-    for (int kt = lo_min / 32; kt <= pos_max / 32; kt++) {
+    int kt_first = lo_min / 32, kt_end = pos_max / 32 + 1;
+    if (EXT && part_ws) {
+      // the keys in sight dealt to the blocks of grid.z in runs of whole tiles (a step of single
+      // tokens: a block has one token, so the run follows from its own first and last key)
+      const int per = (kt_end - kt_first + n_splits - 1) / n_splits;
+      kt_first += (int)blockIdx.z * per;
+      kt_end = min(kt_end, kt_first + per);
+    }
+    for (int kt = kt_first; kt < kt_end; kt++) {
       const int key0 = kt * 32;
       __syncthreads();                        // the tile before has been used by everybody
       {
@@ -109,8 +118,21 @@ attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restri
           const TC* vp = kp ? cache + (size_t)(bt[p / page_size]) * page_elems + (size_t)Hkv * page_size * D +
                                   ((size_t)hk * page_size + p % page_size) * DV
                             : nullptr;
-          for (int d = part; d < D; d += TPK) Ks[j * DP + d] = kp ? to_f32(kp[d]) : 0.0f;
-          for (int d = part; d < DV; d += TPK) Vs[j * DV + d] = vp ? to_f32(vp[d]) : 0.0f;
+          if (D % 4 == 0 && DV % 4 == 0) {      // (rows, pages and both blocks of a page start at multiples of four)
+            for (int d = part * 4; d < D; d += 4 * TPK) {
+              float k4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+              if (kp) load4(kp + d, k4);
+              *reinterpret_cast<float4*>(&Ks[j * DP + d]) = make_float4(k4[0], k4[1], k4[2], k4[3]);
+            }
+            for (int d = part * 4; d < DV; d += 4 * TPK) {
+              float v4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+              if (vp) load4(vp + d, v4);
+              *reinterpret_cast<float4*>(&Vs[j * DV + d]) = make_float4(v4[0], v4[1], v4[2], v4[3]);
+            }
+          } else {
+            for (int d = part; d < D; d += TPK) Ks[j * DP + d] = kp ? to_f32(kp[d]) : 0.0f;
+            for (int d = part; d < DV; d += TPK) Vs[j * DV + d] = vp ? to_f32(vp[d]) : 0.0f;
+          }
         } else if (D % 4 == 0) {
           for (int d = part * 4; d < D; d += 4 * TPK) {
             float k4[4] = {0.0f, 0.0f, 0.0f, 0.0f}, v4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -176,6 +198,19 @@ attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restri
       }
     }
   }
+  if (EXT && part_ws) {
+    // this block's share of the keys: maximum, sum and unnormalised result, for the merge
+    if (mine) {
+      float* rec = part_ws + (((size_t)(t0 + warp) * H + h) * n_splits + blockIdx.z) * (DV + 2);
+      if (lane == 0) { rec[0] = m; rec[1] = l; }
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const int d = lane + 32 * i;
+        if (d < DV) rec[2 + d] = acc[i];
+      }
+    }
+    return;
+  }
   if (mine) {
     TO* op = out + (size_t)(t0 + warp) * o_stride + (size_t)h * DV;
     float inv = 1.0f / l;
@@ -204,7 +239,7 @@ static int attention_simt_run(const void* q, int q_stride, const void* cache,
                               int Hkv, int D, int page_size, float scale, int window,
                               int max_keys, int act_dtype, int cache_dtype, int n_pages, int* err,
                               int max_q_len, int kv_shared, cudaStream_t stream, bool ext = false, int DV = 0,
-                              int chunk = 0, const float* sinks = nullptr) {
+                              int chunk = 0, const float* sinks = nullptr, int n_splits = 1, float* part_ws = nullptr) {
   if (T <= 0) return SGLC_OK;
   if (!ext) DV = D;
   if (DV <= 0 || DV > 256 || chunk < 0) return ext ? SGLC_ERR_UNSUPPORTED : SGLC_ERR_ARGUMENT;
@@ -215,7 +250,8 @@ static int attention_simt_run(const void* q, int q_stride, const void* cache,
   const bool single = max_q_len <= 1;
   const int W = single ? 1 : 8;
   const size_t smem = ((size_t)32 * (D % 4 == 0 ? D + 4 : D + 1) + (size_t)32 * DV + (size_t)W * D + (size_t)W * 32) * sizeof(float);
-  dim3 grid((T + W - 1) / W, H);
+  if (part_ws && (!ext || !single || n_splits < 1 || n_splits > 65535)) return SGLC_ERR_ARGUMENT;
+  dim3 grid((T + W - 1) / W, H, part_ws ? n_splits : 1);
 #define LAUNCH_E(TQ, TC, TO, WW, TH, EX)                                                               \
   do {                                                                                                 \
     if (smem > 48 * 1024)                                                                              \
@@ -224,7 +260,7 @@ static int attention_simt_run(const void* q, int q_stride, const void* cache,
     attention_simt_kernel<TQ, TC, TO, WW, TH, EX><<<grid, TH, smem, stream>>>(                          \
         (const TQ*)q, q_stride, (const TC*)cache, block_table, bt_stride, token_req, positions,        \
         (TO*)out, o_stride, T, H, Hkv, D, page_size, scale, window, n_pages, err, kv_shared, DV,       \
-        chunk, sinks);                                                                                 \
+        chunk, sinks, n_splits, part_ws);                                                              \
   } while (0)
 #define LAUNCH(TQ, TC, TO, WW, TH)                                                                     \
   do {                                                                                                 \
@@ -282,4 +318,58 @@ SGLC_API int sglc_attention_simt_ext(const void* q, int q_stride, const void* ca
   return attention_simt_run(q, q_stride, cache, block_table, bt_stride, token_req, positions, out, o_stride,
                             T, H, Hkv, D, page_size, scale, window, max_keys, act_dtype, cache_dtype,
                             n_pages, err, max_q_len, 0, stream, true, DV, chunk, sinks);
+}
+
+// The merge behind a launch that dealt a token's keys to several blocks (a step of single tokens):
+// the shares' maxima, sums and unnormalised results [T][H][n_splits][DV + 2] become the head's
+// result, the sink (if any) joining the denominator once.  A warp a (token, head).
+template <typename TO>
+__global__ void __launch_bounds__(128)
+attention_merge_kernel(const float* __restrict__ part_ws, int n_splits, const float* __restrict__ sinks,
+                       TO* __restrict__ out, int o_stride, int T, int H, int DV) {
+  pdl_launch_dependents();
+  const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  pdl_wait();
+  if (item >= (long long)T * H) return;
+  const int t = (int)(item / H), h = (int)(item % H);
+  const float* rec = part_ws + (size_t)item * n_splits * (DV + 2);
+  float M = sinks ? sinks[h] : -INFINITY;
+  for (int s = 0; s < n_splits; s++)
+    if (rec[(size_t)s * (DV + 2) + 1] > 0.0f) M = fmaxf(M, rec[(size_t)s * (DV + 2)]);
+  float L = sinks ? expf(sinks[h] - M) : 0.0f;
+  for (int s = 0; s < n_splits; s++) {
+    const float ls = rec[(size_t)s * (DV + 2) + 1];
+    if (ls > 0.0f) L += ls * expf(rec[(size_t)s * (DV + 2)] - M);
+  }
+  const float inv = 1.0f / L;
+  TO* op = out + (size_t)t * o_stride + (size_t)h * DV;
+  for (int d = lane; d < DV; d += 32) {
+    float o = 0.0f;
+    for (int s = 0; s < n_splits; s++)
+      if (rec[(size_t)s * (DV + 2) + 1] > 0.0f) o += rec[(size_t)s * (DV + 2) + 2 + d] * expf(rec[(size_t)s * (DV + 2)] - M);
+    op[d] = from_f32<TO>(o * inv);
+  }
+}
+
+// The extended form for a step of single tokens with each token's keys dealt to n_splits blocks:
+// part_ws holds T x H x n_splits x (DV + 2) floats; two launches (the shares, then the merge).
+SGLC_API int sglc_attention_simt_ext_split(const void* q, int q_stride, const void* cache,
+                                           const int* block_table, int bt_stride, const int* token_req,
+                                           const int* positions, void* out, int o_stride, int T, int H,
+                                           int Hkv, int D, int DV, int page_size, float scale, int window, int chunk,
+                                           const float* sinks, int max_keys, int act_dtype, int cache_dtype,
+                                           int n_pages, int* err, int n_splits, float* part_ws, cudaStream_t stream) {
+  if (T <= 0) return SGLC_OK;
+  if (!part_ws || n_splits < 1) return SGLC_ERR_ARGUMENT;
+  const int code = attention_simt_run(q, q_stride, cache, block_table, bt_stride, token_req, positions, out, o_stride,
+                                      T, H, Hkv, D, page_size, scale, window, max_keys, act_dtype, cache_dtype,
+                                      n_pages, err, 1, 0, stream, true, DV, chunk, nullptr, n_splits, part_ws);
+  if (code != SGLC_OK) return code;
+  const dim3 grid((unsigned)(((long long)T * H + 3) / 4));
+  if (act_dtype == SGLC_F32)
+    return sglc_launch(attention_merge_kernel<float>, grid, dim3(128), 0, stream, 1, true, (const float*)part_ws,
+                       n_splits, sinks, (float*)out, o_stride, T, H, DV);
+  return sglc_launch(attention_merge_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, 1, true,
+                     (const float*)part_ws, n_splits, sinks, (__nv_bfloat16*)out, o_stride, T, H, DV);
 }

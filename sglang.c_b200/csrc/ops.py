@@ -1086,13 +1086,26 @@ def gated_gather(z, tokens, table, first, dst, err_flag=None):
     _check(lib, code, "gated_gather")
 
 
+EXT_MAX_SPLITS = 16         # blocks a token's keys are dealt to at most (attention_ext in a step of single tokens)
+
+
+def attention_ext_splits(max_keys, window=None, chunk=None):
+    """How many blocks share a token's keys in a step of single tokens: two tiles of 32 keys a block,
+    up to EXT_MAX_SPLITS (1: the plain launch)."""
+    seen = min(int(max_keys), int(window or max_keys), int(chunk or max_keys))
+    tiles = (seen + 31) // 32 + 1
+    return max(1, min(EXT_MAX_SPLITS, tiles // 2))
+
+
 def attention_ext(q, cache, block_table, token_req, positions, out, n_heads, n_kv_heads, dim, v_dim, page_size,
-                  scale, window, chunk, sinks, max_keys, max_q_len=None):
+                  scale, window, chunk, sinks, max_keys, max_q_len=None, splits=1, workspace=None):
     """attention_simt's extended form: values of size v_dim beside keys of size dim (cache
     [n_pages, G*page_size*(dim+v_dim)]: a page's keys, then its values), an optional chunk mask
     (a query sees the keys of its own chunk of `chunk` positions) and an optional sink per head
-    (float32 [H]) in the softmax's denominator.  q [T, H*dim]; out [T, H*v_dim]."""
-    _need_cuda(q, cache, block_table, token_req, positions, out, sinks)
+    (float32 [H]) in the softmax's denominator.  q [T, H*dim]; out [T, H*v_dim].
+    splits > 1 (a step of single tokens only): every token's keys are dealt to so many blocks, whose
+    shares a second launch merges; workspace: float32, T * H * splits * (v_dim + 2) entries."""
+    _need_cuda(q, cache, block_table, token_req, positions, out, sinks, workspace)
     for t, nm in ((block_table, "block_table"), (token_req, "token_req"), (positions, "positions")):
         _i32(t, nm)
     T = q.shape[0]
@@ -1105,6 +1118,19 @@ def attention_ext(q, cache, block_table, token_req, positions, out, n_heads, n_k
     if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != n_heads):
         raise KernelError("attention_ext: one float32 sink per head")
     lib = build.load("attention_simt")
+    if splits > 1:
+        if (max_q_len or 2) > 1 or workspace is None or workspace.dtype != torch.float32 \
+                or workspace.numel() < T * n_heads * splits * (v_dim + 2) or not workspace.is_contiguous():
+            raise KernelError("attention_ext: keys are split over blocks in a step of single tokens only, with a "
+                              "float32 workspace of T * H * splits * (v_dim + 2) entries")
+        code = lib.sglc_attention_simt_ext_split(
+            _ptr(q), q.stride(0), _ptr(cache), _ptr(block_table), block_table.stride(0), _ptr(token_req),
+            _ptr(positions), _ptr(out), out.stride(0), T, int(n_heads), int(n_kv_heads), int(dim), int(v_dim),
+            int(page_size), ctypes.c_float(scale), int(window or 0), int(chunk or 0), _ptr(sinks), int(max_keys),
+            _dt(q, "attention q"), _dt(cache, "cache"), n_pages, _ptr(tc_error_flag(q.device)), int(splits),
+            _ptr(workspace), _stream())
+        _check(lib, code, f"attention_ext (head {dim}/{v_dim}, up to {max_keys} keys, {splits} shares)", n_kernels=2)
+        return
     code = lib.sglc_attention_simt_ext(_ptr(q), q.stride(0), _ptr(cache), _ptr(block_table), block_table.stride(0),
                                        _ptr(token_req), _ptr(positions), _ptr(out), out.stride(0), T, int(n_heads),
                                        int(n_kv_heads), int(dim), int(v_dim), int(page_size), ctypes.c_float(scale),

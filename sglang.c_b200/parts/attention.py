@@ -412,7 +412,9 @@ class RotaryAttention(Part):
         p = self.params
         H, G, D, V = p["n_heads"], p["n_kv_heads"], p["head_dim"], p["v_dim"]
         act = 4 if self.rt.dtype == "float32" else 2
-        return 4 * ((H + G) * D + G * V + 8) + act * H * (D + V) + 1024
+        from ..csrc import ops
+        # (a step of single tokens deals a token's keys to several blocks: their shares)
+        return 4 * ((H + G) * D + G * V + 8) + act * H * (D + V) + 1024 + 4 * H * ops.EXT_MAX_SPLITS * (V + 2)
 
     def forward(self, ctx, h, residual, cache, position=None, out=None):
         from ..csrc import ops
@@ -446,9 +448,13 @@ class RotaryAttention(Part):
                 ops.attention_prefill_tc(q, pages, grp.block_table, ctx.q_start, ctx.kv_len, o, H, float(p["scale"]),
                                          p.get("window"), ctx.R, ctx.max_q_len, chunk=p.get("chunk"), sinks=self.sink)
                 return self.out.forward(ctx, o, out=out, residual=residual)
+        # every other step goes to the general kernel; where every request brings one token, a
+        # token's keys are dealt to several blocks and a second launch merges their shares
+        splits = ops.attention_ext_splits(ctx.max_keys, p.get("window"), p.get("chunk")) if ctx.max_q_len == 1 else 1
+        ws = ctx.alloc((T * H * splits * (V + 2),), torch.float32) if splits > 1 else None
         ops.attention_ext(q, cache.tensor, grp.block_table, ctx.token_req, ctx.positions, o, H, G, D, V, grp.page_size,
                           float(p["scale"]), p.get("window"), p.get("chunk"), self.sink, ctx.max_keys,
-                          max_q_len=ctx.max_q_len)
+                          max_q_len=ctx.max_q_len, splits=splits, workspace=ws)
         return self.out.forward(ctx, o, out=out, residual=residual)
 
 

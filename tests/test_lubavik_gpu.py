@@ -145,8 +145,12 @@ def test_attention_behind_it_chunk_edges_sinks_far_keys_and_page_borders(dtype, 
             qo = torch.empty((T, H * D), dtype=dtype, device=DEV)
             ops.qk_prep(xd[lo:hi], i32(pos[lo:hi]), freq, 1.0, dims, pairing, norm, eps, dev(gq), dev(gk), qo, cache,
                         i32(slots[lo:hi]), H, G, D, V, page)
+            # (a single token's keys are dealt to several blocks whose shares a second launch merges)
+            splits = ops.attention_ext_splits(hi, None, chunk) if T == 1 else 1
+            assert T > 1 or chunk is not None and chunk < 64 or hi <= 64 or splits > 1
+            ws = torch.empty(T * H * splits * (V + 2), device=DEV) if splits > 1 else None
             ops.attention_ext(qo, cache, i32(table[None, :]), i32([0] * T), i32(pos[lo:hi]), out[lo:hi], H, G, D, V, page,
-                              scale, None, chunk, dev(sk) if sinks else None, hi, max_q_len=T)
+                              scale, None, chunk, dev(sk) if sinks else None, hi, max_q_len=T, splits=splits, workspace=ws)
         assert np.abs(out.float().cpu().numpy().reshape(n, H, V) - want).max() < tol, first
 
 
