@@ -435,12 +435,23 @@ stabilized_gates_kernel(const float* __restrict__ xi, long long xi_stride, const
   if (t1 <= t0 || !sglc_index_ok(slot, n_slots, err)) return;
   float m_in = m_state[(size_t)slot * H + h];
   const float inv_cap = 1.0f / cap;
+  // (the next round's pre-activations are asked for before this round's arithmetic: a round then
+  // costs its chain of shuffles and exponentials, not a trip to memory on top)
+  float zi_next = 0.0f, zf_next = 0.0f;
+  if (t0 + lane < t1) {
+    zi_next = xi[(size_t)(t0 + lane) * xi_stride + h];
+    zf_next = xf[(size_t)(t0 + lane) * xf_stride + h];
+  }
   for (int tb = t0; tb < t1; tb += 32) {
     const int t = tb + lane;
     const bool on = t < t1;
     float f = 0.0f, i = -INFINITY;            // beyond the end: the identity of the scan
+    const float zi = zi_next, zf = zf_next;
+    if (t + 32 < t1) {
+      zi_next = xi[(size_t)(t + 32) * xi_stride + h];
+      zf_next = xf[(size_t)(t + 32) * xf_stride + h];
+    }
     if (on) {
-      const float zi = xi[(size_t)t * xi_stride + h], zf = xf[(size_t)t * xf_stride + h];
       i = cap * tanhf(zi * inv_cap);
       const float u = cap * tanhf(zf * inv_cap);
       f = -(fmaxf(-u, 0.0f) + log1pf(expf(-fabsf(u))));
