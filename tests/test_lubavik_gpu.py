@@ -154,6 +154,62 @@ def test_attention_behind_it_chunk_edges_sinks_far_keys_and_page_borders(dtype, 
         assert np.abs(out.float().cpu().numpy().reshape(n, H, V) - want).max() < tol, first
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("chunk", [None, 200, 48])
+def test_one_key_that_stands_out_far_back_and_at_the_chunks_edge(dtype, chunk):
+    """Among hundreds of small keys one is made to carry nearly all the weight of the last query:
+    a key far back (position 3) without chunks, or the first key of the query's chunk (just inside:
+    it must count) and the key one place before it (just outside: it must not).  Prompt in one
+    portion and the last token alone (its keys dealt to blocks and merged); pages shuffled; a sink
+    large enough to take a known share."""
+    from sglang_c_b200.csrc import ops
+    rng = np.random.default_rng(chunk or 1)
+    n, H, G, D, V, page = 457, 4, 2, 16, 24, 16
+    q = rng.standard_normal((n, H, D)) * 0.1
+    k = rng.standard_normal((n, G, D)) * 0.1
+    v = rng.standard_normal((n, G, V))
+    direction = rng.standard_normal(D)
+    direction /= np.linalg.norm(direction)
+    q[-1] = 3.0 * direction                                     # every head of the last query
+    start = ((n - 1) // chunk) * chunk if chunk else 0
+    inside, outside = (start, start - 1) if chunk else (3, None)
+    sinks = np.full(H, 2.0)
+    for which in ("inside", "outside"):
+        if which == "outside" and outside is None:
+            continue
+        kk = k.copy()
+        kk[inside if which == "inside" else outside] = 3.0 * direction        # score 9 against scores of about 0.05
+        want = P.softmax_attention(q, kk, v, 1.0, chunk=chunk, sinks=sinks)
+        if which == "inside":       # the key carries most of the last query's weight (the rest: the sink and the crowd)
+            share = math.exp(9.0) / (math.exp(9.0) + math.exp(2.0) + (n - start))
+            assert share > 0.9 and np.abs(want[-1, 0] - share * v[inside, 0]).max() < 0.2
+        else:
+            assert np.abs(want[-1]).max() < 0.5 * np.abs(v[outside]).max()
+        x = dev(np.concatenate([q.reshape(n, -1), kk.reshape(n, -1), v.reshape(n, -1)], 1))
+        if dtype == torch.bfloat16:
+            x = x.to(dtype).float()
+            f64 = lambda t: t.cpu().numpy().astype(np.float64)
+            want = P.softmax_attention(f64(x[:, :H * D]).reshape(n, H, D), f64(x[:, H * D:(H + G) * D]).reshape(n, G, D),
+                                       f64(x[:, (H + G) * D:]).reshape(n, G, V), 1.0, chunk=chunk, sinks=sinks)
+        n_pages = (n + page - 1) // page + 2
+        table = rng.permutation(n_pages)[:(n + page - 1) // page]
+        pos = np.arange(n)
+        slots = table[pos // page] * page + pos % page
+        cache = torch.zeros((n_pages, G * page * (D + V)), dtype=dtype, device=DEV)
+        out = torch.zeros((n, H * V), dtype=dtype, device=DEV)
+        for lo, hi in ((0, n - 1), (n - 1, n)):
+            T = hi - lo
+            qo = torch.empty((T, H * D), dtype=dtype, device=DEV)
+            ops.qk_prep(x[lo:hi], i32(pos[lo:hi]), None, 1.0, 0, "halves", None, 0.0, None, None, qo, cache, i32(slots[lo:hi]),
+                        H, G, D, V, page)
+            splits = ops.attention_ext_splits(hi, None, chunk) if T == 1 else 1
+            ws = torch.empty(T * H * splits * (V + 2), device=DEV) if splits > 1 else None
+            ops.attention_ext(qo, cache, i32(table[None, :]), i32([0] * T), i32(pos[lo:hi]), out[lo:hi], H, G, D, V, page,
+                              1.0, None, chunk, dev(sinks), hi, max_q_len=T, splits=splits, workspace=ws)
+        got = out.float().cpu().numpy().reshape(n, H, V)
+        assert np.abs(got - want).max() < (1e-4 if dtype == torch.float32 else 2e-2), which
+
+
 def _glu_inputs(rng, n, H, D, V, near_one):
     q, k = rng.standard_normal((n, H * D)), rng.standard_normal((n, H * D))
     v = rng.standard_normal((n, H * V))
@@ -511,7 +567,8 @@ def test_greedy_generation_through_the_scheduler(dirs, name, dtype):
     assert st.n_finished == len(prompts) and st.pool_free == st.pool_pages
 
 
-def test_the_decays_rank_comes_from_the_file(dirs, tmp_path):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_decays_rank_comes_from_the_file(dirs, tmp_path, dtype):
     """The low-rank pair of the decays has whatever rank its tensors have."""
     import json
     import os
@@ -526,15 +583,16 @@ def test_the_decays_rank_comes_from_the_file(dirs, tmp_path):
             a = (rng.standard_normal((3, a.shape[1])) * 0.3).astype(np.float32)
         elif k.endswith("right.a2"):
             a = (rng.standard_normal((a.shape[0], 3)) * 0.5).astype(np.float32)
-        tensors[k] = torch.from_numpy(a)
+        t = torch.from_numpy(a)
+        tensors[k] = t.to(torch.bfloat16) if (dtype == "bfloat16" and t.dim() >= 2) else t
     d = str(tmp_path / "rank3")
     os.makedirs(d)
     with open(os.path.join(d, "config.json"), "w") as f:
         json.dump(cfg, f)
     write_safetensors(os.path.join(d, "model.safetensors"), tensors, metadata={"format": "pt"})
     reqs = {"a": traces.random_tokens(1, 70, LUB["C"]["vocab"])}
-    got, _ = run_trace(d, "float32", "C", traces.portions(reqs), tmp_path)
-    check_errors(got, reference(d, reqs), "float32", "rank 3")
+    got, _ = run_trace(d, dtype, "C", traces.portions(reqs), tmp_path)
+    check_errors(got, reference(d, reqs), dtype, "rank 3")
 
 
 def test_command_line_generates_from_a_random_folder(tmp_path):
