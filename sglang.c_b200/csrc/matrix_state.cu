@@ -435,8 +435,8 @@ stabilized_gates_kernel(const float* __restrict__ xi, long long xi_stride, const
   if (t1 <= t0 || !sglc_index_ok(slot, n_slots, err)) return;
   float m_in = m_state[(size_t)slot * H + h];
   const float inv_cap = 1.0f / cap;
-  // (the next round's pre-activations are asked for before this round's arithmetic: a round then
-  // costs its chain of shuffles and exponentials, not a trip to memory on top)
+  // (the next 32 tokens' pre-activations are asked for before these tokens' arithmetic: a batch
+  // then costs its chain of shuffles and exponentials, not a trip to memory on top)
   float zi_next = 0.0f, zf_next = 0.0f;
   if (t0 + lane < t1) {
     zi_next = xi[(size_t)(t0 + lane) * xi_stride + h];
