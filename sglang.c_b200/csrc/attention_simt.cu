@@ -42,8 +42,13 @@ attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restri
                       TO* __restrict__ out, int o_stride, int T, int H, int Hkv, int D, int page_size,
                       float scale, int window, int n_pages, int* err, int kv_shared,
                       int DV_arg, int chunk, const float* __restrict__ sinks, int n_splits,
-                      float* __restrict__ part_ws) {
+                      float* __restrict__ part_ws, int head_rows) {
   const int DV = EXT ? DV_arg : D;
+  // head_rows (EXT, a step of single tokens): the block's warps are the query heads that share one
+  // key/value head, all of ONE token (blockIdx.x), instead of consecutive tokens of one head: the
+  // tile of keys and values is staged once for all of them
+  const bool hrows = EXT && head_rows;
+  const int grp = H / Hkv;
   extern __shared__ __align__(16) float smem[];
   __shared__ int s_req[W], s_lo[W], s_pos[W];
   // padded key rows: a lane a key without bank conflicts (by 4 where rows are read 16 bytes at a time)
@@ -54,11 +59,13 @@ attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restri
   float* pw = Vs + 32 * DV;                   // [W][32]: a tile's weights (16-byte aligned whatever D is)
   float* qs = pw + W * 32;                    // [W][D]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int h = blockIdx.y, hk = h / (H / Hkv);
-  const int t0 = blockIdx.x * W;
+  const int hk = hrows ? (int)blockIdx.y : (int)blockIdx.y / grp;
+  const int h = hrows ? hk * grp + min(warp, grp - 1) : (int)blockIdx.y;      // this warp's query head
+  const int t0 = hrows ? (int)blockIdx.x : (int)blockIdx.x * W;
+  const int my_t = hrows ? t0 : t0 + warp;                                     // this warp's token
   if (tid < W) {
-    const int t = t0 + tid;
-    const bool on = t < T;
+    const int t = hrows ? t0 : t0 + tid;
+    const bool on = hrows ? tid < grp : t < T;
     const int pos = on ? positions[t] : -1;
     s_req[tid] = on ? token_req[t] : -1;
     s_pos[tid] = pos;
@@ -66,12 +73,12 @@ attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restri
     if (EXT && chunk > 0 && pos >= 0) lo = max(lo, pos / chunk * chunk);
     s_lo[tid] = lo;
   }
-  if (warp < W && t0 + warp < T) {
-    const TQ* qp = q + (size_t)(t0 + warp) * q_stride + (size_t)h * D;
+  const bool mine = warp < W && (hrows ? warp < grp : t0 + warp < T);
+  if (mine) {
+    const TQ* qp = q + (size_t)my_t * q_stride + (size_t)h * D;
     for (int d = lane; d < D; d += 32) qs[warp * D + d] = to_f32(qp[d]);
   }
   __syncthreads();
-  const bool mine = warp < W && t0 + warp < T;
   const int my_req = mine ? s_req[warp] : -2, my_lo = mine ? s_lo[warp] : 0, my_pos = mine ? s_pos[warp] : -1;
   float m = -INFINITY, l = 0.0f;
   float acc[8];                               // dims lane, lane + 32, ... of the output
@@ -201,7 +208,7 @@ attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restri
   if (EXT && part_ws) {
     // this block's share of the keys: maximum, sum and unnormalised result, for the merge
     if (mine) {
-      float* rec = part_ws + (((size_t)(t0 + warp) * H + h) * n_splits + blockIdx.z) * (DV + 2);
+      float* rec = part_ws + (((size_t)my_t * H + h) * n_splits + blockIdx.z) * (DV + 2);
       if (lane == 0) { rec[0] = m; rec[1] = l; }
 #pragma unroll
       for (int i = 0; i < 8; i++) {
@@ -212,7 +219,7 @@ attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restri
     return;
   }
   if (mine) {
-    TO* op = out + (size_t)(t0 + warp) * o_stride + (size_t)h * DV;
+    TO* op = out + (size_t)my_t * o_stride + (size_t)h * DV;
     float inv = 1.0f / l;
     if (EXT && sinks) {                        // the sink joins the denominator: exp(sink - max) once
       const float sk = sinks[h], m_all = fmaxf(m, sk);
@@ -252,6 +259,28 @@ static int attention_simt_run(const void* q, int q_stride, const void* cache,
   const size_t smem = ((size_t)32 * (D % 4 == 0 ? D + 4 : D + 1) + (size_t)32 * DV + (size_t)W * D + (size_t)W * 32) * sizeof(float);
   if (part_ws && (!ext || !single || n_splits < 1 || n_splits > 65535)) return SGLC_ERR_ARGUMENT;
   dim3 grid((T + W - 1) / W, H, part_ws ? n_splits : 1);
+  // single tokens whose shares are merged afterwards: where 2 to 8 query heads share a key/value
+  // head, a block takes them all (the eight-warp form, its warps being heads of one token)
+  const int head_rows = (part_ws && H / Hkv >= 2 && H / Hkv <= 8) ? 1 : 0;
+  const size_t smem_rows = ((size_t)32 * (D % 4 == 0 ? D + 4 : D + 1) + (size_t)32 * DV + (size_t)8 * D + (size_t)8 * 32) * sizeof(float);
+  if (head_rows) {
+    const dim3 grid_rows(T, Hkv, n_splits);
+#define LAUNCH_R(TQ, TC, TO)                                                                            \
+  do {                                                                                                 \
+    if (smem_rows > 48 * 1024)                                                                         \
+      cudaFuncSetAttribute(attention_simt_kernel<TQ, TC, TO, 8, 256, true>,                            \
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_rows);               \
+    attention_simt_kernel<TQ, TC, TO, 8, 256, true><<<grid_rows, 256, smem_rows, stream>>>(            \
+        (const TQ*)q, q_stride, (const TC*)cache, block_table, bt_stride, token_req, positions,        \
+        (TO*)out, o_stride, T, H, Hkv, D, page_size, scale, window, n_pages, err, kv_shared, DV,       \
+        chunk, sinks, n_splits, part_ws, 1);                                                           \
+  } while (0)
+    if (act_dtype == SGLC_F32 && cache_dtype == SGLC_F32) LAUNCH_R(float, float, float);
+    else if (act_dtype == SGLC_BF16 && cache_dtype == SGLC_BF16) LAUNCH_R(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+    else return SGLC_ERR_ARGUMENT;
+#undef LAUNCH_R
+    return sglc_launch_status();
+  }
 #define LAUNCH_E(TQ, TC, TO, WW, TH, EX)                                                               \
   do {                                                                                                 \
     if (smem > 48 * 1024)                                                                              \
@@ -260,7 +289,7 @@ static int attention_simt_run(const void* q, int q_stride, const void* cache,
     attention_simt_kernel<TQ, TC, TO, WW, TH, EX><<<grid, TH, smem, stream>>>(                          \
         (const TQ*)q, q_stride, (const TC*)cache, block_table, bt_stride, token_req, positions,        \
         (TO*)out, o_stride, T, H, Hkv, D, page_size, scale, window, n_pages, err, kv_shared, DV,       \
-        chunk, sinks, n_splits, part_ws);                                                              \
+        chunk, sinks, n_splits, part_ws, 0);                                                           \
   } while (0)
 #define LAUNCH(TQ, TC, TO, WW, TH)                                                                     \
   do {                                                                                                 \
