@@ -188,15 +188,17 @@ SGLC_API int sglc_latent_rope(const float* qx, long long qx_stride, const float*
 // (G x page_size x D keys, then G x page_size x V values) at slots[t]; values are multiplied by
 // v_mult on the way (a mixer whose result is a fixed multiple of the attention's folds it here:
 // the attention is linear in its values).  eps lies inside every root.
+constexpr int QK_WARPS = 8;      // (a token's head rows are dealt to the warps: eight keep the rounds few)
+
 template <typename TA>
-__global__ void __launch_bounds__(ROT_WARPS * 32)
+__global__ void __launch_bounds__(QK_WARPS * 32)
 qk_prep_kernel(const float* __restrict__ x, long long x_stride, const int* __restrict__ positions,
                const double* __restrict__ freq, float mult, int dims, int pairing, int norm_mode, float eps,
                const float* __restrict__ gain_q, const float* __restrict__ gain_k, float v_mult,
                TA* __restrict__ q_out, long long q_stride, TA* __restrict__ cache, const int* __restrict__ slots,
                int T, int H, int G, int D, int V, int page_size, int n_pages, int* err) {
-  __shared__ float buf[ROT_WARPS][ROT_MAX_DIM];
-  __shared__ float red[2][ROT_WARPS];
+  __shared__ float buf[QK_WARPS][ROT_MAX_DIM];
+  __shared__ float red[2][QK_WARPS];
   pdl_launch_dependents();
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_wait();
@@ -212,19 +214,19 @@ qk_prep_kernel(const float* __restrict__ x, long long x_stride, const int* __res
     // one root mean square over all query heads, one over all key heads: every thread sums its
     // share in a fixed order, so a token's bits do not depend on the rest of the step
     float sq = 0.0f, sk = 0.0f;
-    for (int i = threadIdx.x; i < H * D; i += ROT_WARPS * 32) sq = fmaf(xr[i], xr[i], sq);
-    for (int i = threadIdx.x; i < G * D; i += ROT_WARPS * 32) sk = fmaf(xr[H * D + i], xr[H * D + i], sk);
+    for (int i = threadIdx.x; i < H * D; i += QK_WARPS * 32) sq = fmaf(xr[i], xr[i], sq);
+    for (int i = threadIdx.x; i < G * D; i += QK_WARPS * 32) sk = fmaf(xr[H * D + i], xr[H * D + i], sk);
     sq = warp_sum(sq);
     sk = warp_sum(sk);
     if (lane == 0) { red[0][warp] = sq; red[1][warp] = sk; }
     __syncthreads();
     sq = 0.0f; sk = 0.0f;
-    for (int w = 0; w < ROT_WARPS; w++) { sq += red[0][w]; sk += red[1][w]; }
+    for (int w = 0; w < QK_WARPS; w++) { sq += red[0][w]; sk += red[1][w]; }
     inv_all[0] = 1.0f / sqrtf(sq / (float)(H * D) + eps);
     if (G > 0) inv_all[1] = 1.0f / sqrtf(sk / (float)(G * D) + eps);
   }
   float* b = buf[warp];
-  for (int row = warp; row < H + 2 * G; row += ROT_WARPS) {
+  for (int row = warp; row < H + 2 * G; row += QK_WARPS) {
     if (row >= H + G) {                        // a value head: copied (times v_mult)
       const int g = row - H - G;
       if (page_ok) {
@@ -297,11 +299,11 @@ SGLC_API int sglc_qk_prep(const float* x, long long x_stride, const int* positio
   if (dims > 0 && !freq) return SGLC_ERR_ARGUMENT;
   if (D > ROT_MAX_DIM) return SGLC_ERR_UNSUPPORTED;
   if (dtype == SGLC_F32)
-    return sglc_launch(qk_prep_kernel<float>, dim3(T), dim3(ROT_WARPS * 32), 0, stream, 1, true, x, x_stride, positions,
+    return sglc_launch(qk_prep_kernel<float>, dim3(T), dim3(QK_WARPS * 32), 0, stream, 1, true, x, x_stride, positions,
                        freq, mult, dims, pairing, norm_mode, eps, gain_q, gain_k, v_mult, (float*)q_out, q_stride,
                        (float*)cache, slots, T, H, G, D, V, page_size, n_pages, err);
   if (dtype == SGLC_BF16)
-    return sglc_launch(qk_prep_kernel<__nv_bfloat16>, dim3(T), dim3(ROT_WARPS * 32), 0, stream, 1, true, x, x_stride,
+    return sglc_launch(qk_prep_kernel<__nv_bfloat16>, dim3(T), dim3(QK_WARPS * 32), 0, stream, 1, true, x, x_stride,
                        positions, freq, mult, dims, pairing, norm_mode, eps, gain_q, gain_k, v_mult,
                        (__nv_bfloat16*)q_out, q_stride, (__nv_bfloat16*)cache, slots, T, H, G, D, V, page_size, n_pages,
                        err);
