@@ -288,6 +288,9 @@ class GatedLinearAttention(Part):
         H, D, V = p["n_heads"], p["dim"], p["v_dim"]
         refs = [tensors[k] for k in ("q_weight", "k_weight", "v_weight", "gate_weight", "decay_down")]
         self.rank = refs[-1].tensor.shape[0]
+        if tuple(tensors["decay_up"].tensor.shape) != (H * D, self.rank):
+            raise ValueError(f"gated_linear_attention: the decays' factors are [{self.rank}, size] and "
+                             f"{list(tensors['decay_up'].tensor.shape)}: their ranks differ")
         n = 2 * H * D + 2 * H * V + self.rank
         pad = (-n) % 8
         self.inp = Linear(store.computed("+".join(r.name for r in refs) + f"+{pad}", lambda: torch.cat(

@@ -39,15 +39,6 @@ def i32(a):
     return torch.tensor(np.asarray(a), dtype=torch.int32, device=DEV)
 
 
-def cuts_of(n, sizes):
-    out, lo, k = [], 0, 0
-    while lo < n:
-        hi = min(n, lo + sizes[k % len(sizes)])
-        out.append((lo, hi))
-        lo, k = hi, k + 1
-    return out
-
-
 # ---------------------------------------------------------------------------- mechanisms
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("norm,pairing,H,G,D,V,dims", [
